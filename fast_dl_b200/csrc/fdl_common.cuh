@@ -1,0 +1,142 @@
+// Shared device/host helpers of the sm_100a kernel library.
+//
+// Everything on this path is HBM-bandwidth bound, so the helpers here are about moving
+// bytes: 128-bit streaming loads/stores, warp/block reductions, launch sizing in whole
+// multiples of the SM count, and bounded mbarrier waits for the bulk-async pipelines.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/fdl_kernels.h"
+
+namespace fdl {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---- host side -----------------------------------------------------------------------
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+};
+
+// Properties of the current device (cached per device index).  Returns nullptr and
+// sets *status when the runtime cannot be queried.
+const DeviceInfo* current_device_info(int* status);
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+// Status of the launch that was just enqueued on this thread.
+inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Per-device workspace the library owns (allocated on first use, grown on demand,
+// never freed before process exit).  Used when a caller passes scratch == NULL.
+int get_workspace(size_t bytes, void** out);
+
+// Persistent-grid size: enough blocks to fill every SM `blocks_per_sm` times, but never
+// more than the work needs.
+inline int persistent_grid(const DeviceInfo* info, int blocks_per_sm, int64_t work_blocks) {
+    int64_t cap = static_cast<int64_t>(info->sm_count) * blocks_per_sm;
+    int64_t g = work_blocks < cap ? work_blocks : cap;
+    return g < 1 ? 1 : static_cast<int>(g);
+}
+
+// ---- device side -----------------------------------------------------------------------
+
+#ifdef __CUDACC__
+
+// Streaming (evict-first) 128-bit accesses: every byte on this path is touched once.
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+    return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+    return v;
+}
+
+// ---- mbarrier + 1-D bulk-async copy (TMA engine, non-multicast form only) ----------------
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals)
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Orders generic-proxy smem accesses before later async-proxy (bulk copy) accesses.
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait: gives up after kMbarSpinLimit polls so a lost copy can never hang the
+// GPU.  Returns false on timeout; the caller records an error flag and leaves.
+constexpr uint32_t kMbarSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
+// global -> shared::cta bulk copy of `bytes` (multiple of 16; both addresses 16-B
+// aligned), completion counted on `bar`.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_addr(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+
+#endif  // __CUDACC__
+
+}  // namespace fdl

@@ -1,0 +1,522 @@
+// Elementwise, fused-chain and broadcast-binary kernels (fp32, HBM-bound).
+//
+// One streaming template serves every same-shape op: a persistent grid (a whole multiple
+// of the SM count) walks the tensor tile by tile; each thread issues all of a tile's
+// 128-bit loads before it computes, so a full SM keeps ~256 KiB of reads in flight.
+// Loads and stores carry the evict-first hint because every byte is touched once.
+//
+// The broadcast kernel uses the same tile walk over the OUTPUT and turns each linear
+// index into operand offsets with multiply-high "fast division" constants that the host
+// derives from the collapsed shape, so the device never executes an integer divide
+// (the reference's row-bias kernel pays one `%` per element, src/kernels/cuda/bias.cu:10).
+#include "fdl_common.cuh"
+
+namespace fdl {
+
+namespace {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+constexpr int kMaxOuterDims = 7;
+
+// ---- packs: W consecutive floats moved with one instruction ------------------------------
+
+template <int W>
+struct Pack {
+    float v[W];
+};
+
+template <int W>
+__device__ __forceinline__ Pack<W> load_pack(const float* base, int64_t pack_index);
+
+template <>
+__device__ __forceinline__ Pack<4> load_pack<4>(const float* base, int64_t i) {
+    const float4 t = ld_stream(reinterpret_cast<const float4*>(base) + i);
+    return Pack<4>{{t.x, t.y, t.z, t.w}};
+}
+
+template <>
+__device__ __forceinline__ Pack<1> load_pack<1>(const float* base, int64_t i) {
+    return Pack<1>{{ld_stream(base + i)}};
+}
+
+template <int W>
+__device__ __forceinline__ void store_pack(float* base, int64_t pack_index, const Pack<W>& p);
+
+template <>
+__device__ __forceinline__ void store_pack<4>(float* base, int64_t i, const Pack<4>& p) {
+    st_stream(reinterpret_cast<float4*>(base) + i, make_float4(p.v[0], p.v[1], p.v[2], p.v[3]));
+}
+
+template <>
+__device__ __forceinline__ void store_pack<1>(float* base, int64_t i, const Pack<1>& p) {
+    st_stream(base + i, p.v[0]);
+}
+
+template <int W>
+__device__ __forceinline__ Pack<W> splat(float s) {
+    Pack<W> p;
+#pragma unroll
+    for (int k = 0; k < W; ++k) p.v[k] = s;
+    return p;
+}
+
+// ---- scalar functors.  Explicit _rn intrinsics keep nvcc from contracting a*b+c. ---------
+
+struct AddFn {
+    __device__ __forceinline__ float operator()(float a, float b, float) const {
+        return __fadd_rn(a, b);
+    }
+};
+struct SubFn {
+    __device__ __forceinline__ float operator()(float a, float b, float) const {
+        return __fsub_rn(a, b);
+    }
+};
+struct MulFn {
+    __device__ __forceinline__ float operator()(float a, float b, float) const {
+        return __fmul_rn(a, b);
+    }
+};
+struct DivFn {
+    __device__ __forceinline__ float operator()(float a, float b, float) const {
+        return __fdiv_rn(a, b);
+    }
+};
+struct AddReluFn {
+    __device__ __forceinline__ float operator()(float a, float b, float) const {
+        return fmaxf(0.0f, __fadd_rn(a, b));
+    }
+};
+struct MulAddReluFn {
+    __device__ __forceinline__ float operator()(float a, float b, float c) const {
+        return fmaxf(0.0f, __fadd_rn(__fmul_rn(a, b), c));
+    }
+};
+struct ReluFn {
+    __device__ __forceinline__ float operator()(float x, float, float) const {
+        return fmaxf(0.0f, x);
+    }
+};
+struct LeakyReluFn {
+    float alpha;
+    __device__ __forceinline__ float operator()(float x, float, float) const {
+        return x > 0.0f ? x : __fmul_rn(alpha, x);
+    }
+};
+// Same expression shape as the reference kernel (src/kernels/cuda/activation.cu:45-51),
+// compiled with the same default contraction, so the bits match its GPU output.
+struct GeluFn {
+    __device__ __forceinline__ float operator()(float x, float, float) const {
+        return 0.5f * x * (1.0f + tanhf(0.79788456f * (x + 0.044715f * x * x * x)));
+    }
+};
+struct SigmoidFn {
+    __device__ __forceinline__ float operator()(float x, float, float) const {
+        return 1.0f / (1.0f + expf(-x));
+    }
+};
+struct TanhFn {
+    __device__ __forceinline__ float operator()(float x, float, float) const { return tanhf(x); }
+};
+
+template <int W, class F>
+__device__ __forceinline__ Pack<W> apply(const F& f, const Pack<W>& a, const Pack<W>& b,
+                                         const Pack<W>& c) {
+    Pack<W> r;
+#pragma unroll
+    for (int k = 0; k < W; ++k) r.v[k] = f(a.v[k], b.v[k], c.v[k]);
+    return r;
+}
+
+// ---- same-shape streaming map --------------------------------------------------------------
+
+template <int W, int NIN, class F>
+__global__ void __launch_bounds__(kEwThreads)
+map_kernel(F f, const float* in0, const float* in1, const float* in2, float* out, int64_t npack,
+           int64_t n) {
+    constexpr int64_t kTile = static_cast<int64_t>(kEwThreads) * kEwUnroll;
+    const int64_t full_tiles = npack / kTile;
+    int64_t t = blockIdx.x;
+    for (; t < full_tiles; t += gridDim.x) {
+        const int64_t base = t * kTile + threadIdx.x;
+        Pack<W> x0[kEwUnroll], x1[kEwUnroll], x2[kEwUnroll];
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; ++u) {
+            const int64_t i = base + u * kEwThreads;
+            x0[u] = load_pack<W>(in0, i);
+            if (NIN > 1) x1[u] = load_pack<W>(in1, i);
+            if (NIN > 2) x2[u] = load_pack<W>(in2, i);
+        }
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; ++u) {
+            const int64_t i = base + u * kEwThreads;
+            if (NIN < 2) x1[u] = x0[u];
+            if (NIN < 3) x2[u] = x0[u];
+            store_pack<W>(out, i, apply<W>(f, x0[u], x1[u], x2[u]));
+        }
+    }
+    // Exactly one block leaves the loop with t == full_tiles; it owns the ragged end.
+    if (t == full_tiles) {
+        for (int64_t i = full_tiles * kTile + threadIdx.x; i < npack; i += kEwThreads) {
+            Pack<W> a = load_pack<W>(in0, i);
+            Pack<W> b = NIN > 1 ? load_pack<W>(in1, i) : a;
+            Pack<W> c = NIN > 2 ? load_pack<W>(in2, i) : a;
+            store_pack<W>(out, i, apply<W>(f, a, b, c));
+        }
+        for (int64_t i = npack * W + threadIdx.x; i < n; i += kEwThreads) {
+            const float a = in0[i];
+            const float b = NIN > 1 ? in1[i] : a;
+            const float c = NIN > 2 ? in2[i] : a;
+            out[i] = f(a, b, c);
+        }
+    }
+}
+
+template <int W, int NIN, class F>
+int launch_map_w(const F& f, const float* in0, const float* in1, const float* in2, float* out,
+                 int64_t n, cudaStream_t stream) {
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+    static int blocks_per_sm = 0;  // same for every device this build targets
+    if (blocks_per_sm == 0) {
+        int nb = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &nb, map_kernel<W, NIN, F>, kEwThreads, 0);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        blocks_per_sm = nb > 0 ? nb : 1;
+    }
+    const int64_t npack = n / W;
+    const int64_t tiles = npack / (static_cast<int64_t>(kEwThreads) * kEwUnroll) + 1;
+    const int grid = persistent_grid(info, blocks_per_sm, tiles);
+    map_kernel<W, NIN, F><<<grid, kEwThreads, 0, stream>>>(f, in0, in1, in2, out, npack, n);
+    return launch_status();
+}
+
+template <int NIN, class F>
+int launch_map(const F& f, const float* in0, const float* in1, const float* in2, float* out,
+               int64_t n, cudaStream_t stream) {
+    if (n == 0) return FDL_OK;
+    const bool vec = aligned16(in0) && aligned16(out) && (NIN < 2 || aligned16(in1)) &&
+                     (NIN < 3 || aligned16(in2));
+    return vec ? launch_map_w<4, NIN, F>(f, in0, in1, in2, out, n, stream)
+               : launch_map_w<1, NIN, F>(f, in0, in1, in2, out, n, stream);
+}
+
+// ---- broadcast binary ------------------------------------------------------------------------
+
+// q = n / d for 0 <= n < 2^31 without a divide: q = (mulhi(n, magic) + n) >> shift.
+struct FastDiv {
+    uint32_t d;
+    uint32_t magic;
+    uint32_t shift;
+};
+
+FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    uint32_t shift = 0;
+    while ((uint64_t{1} << shift) < d) ++shift;
+    f.shift = shift;
+    f.magic = static_cast<uint32_t>((((uint64_t{1} << shift) - d) << 32) / d + 1);
+    return f;
+}
+
+__device__ __forceinline__ uint32_t fast_divide(uint32_t n, const FastDiv& f) {
+    return (__umulhi(n, f.magic) + n) >> f.shift;
+}
+
+// Host-precomputed description of one broadcast launch.  The innermost collapsed
+// dimension is walked in packs of W floats; the remaining ("outer") dimensions are
+// peeled innermost-first with fast division.  Strides are in elements; 0 = broadcast.
+struct BroadcastPlan {
+    FastDiv inner_div;  // by the number of packs in the innermost dimension
+    int nouter;
+    FastDiv outer_div[kMaxOuterDims];
+    int64_t a_outer[kMaxOuterDims];
+    int64_t b_outer[kMaxOuterDims];
+    int64_t a_inner;  // element stride of a along the innermost dimension
+    int64_t b_inner;
+    uint32_t total_packs;
+};
+
+template <int W>
+__device__ __forceinline__ Pack<W> load_operand(const float* base, int64_t offset,
+                                                int64_t inner_stride) {
+    if (W == 1) return Pack<W>{{ld_stream(base + offset)}};
+    // W == 4: the host guarantees inner_stride is 1 (vector load) or 0 (splat).
+    if (inner_stride != 0) return load_pack<W>(base + offset, 0);
+    // A value shared by the whole pack is re-read by many threads: default caching.
+    return splat<W>(base[offset]);
+}
+
+template <int W>
+__device__ __forceinline__ void decompose(const BroadcastPlan& plan, uint32_t item,
+                                          int64_t* a_off, int64_t* b_off) {
+    uint32_t outer = fast_divide(item, plan.inner_div);
+    const uint32_t ip = item - outer * plan.inner_div.d;
+    int64_t ao = static_cast<int64_t>(ip) * W * plan.a_inner;
+    int64_t bo = static_cast<int64_t>(ip) * W * plan.b_inner;
+#pragma unroll
+    for (int k = 0; k < kMaxOuterDims; ++k) {
+        if (k < plan.nouter) {
+            uint32_t idx = outer;
+            if (k + 1 < plan.nouter) {
+                const uint32_t q = fast_divide(outer, plan.outer_div[k]);
+                idx = outer - q * plan.outer_div[k].d;
+                outer = q;
+            }
+            ao += static_cast<int64_t>(idx) * plan.a_outer[k];
+            bo += static_cast<int64_t>(idx) * plan.b_outer[k];
+        }
+    }
+    *a_off = ao;
+    *b_off = bo;
+}
+
+template <int W, class F>
+__global__ void __launch_bounds__(kEwThreads)
+broadcast_kernel(F f, const __grid_constant__ BroadcastPlan plan, const float* a, const float* b,
+                 float* out) {
+    constexpr uint32_t kTile = kEwThreads * kEwUnroll;
+    const uint32_t total = plan.total_packs;
+    for (uint32_t base = blockIdx.x * kTile; base < total; base += gridDim.x * kTile) {
+        Pack<W> xa[kEwUnroll], xb[kEwUnroll];
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; ++u) {
+            const uint32_t item = base + u * kEwThreads + threadIdx.x;
+            if (item < total) {
+                int64_t ao, bo;
+                decompose<W>(plan, item, &ao, &bo);
+                xa[u] = load_operand<W>(a, ao, plan.a_inner);
+                xb[u] = load_operand<W>(b, bo, plan.b_inner);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; ++u) {
+            const uint32_t item = base + u * kEwThreads + threadIdx.x;
+            if (item < total) store_pack<W>(out, item, apply<W>(f, xa[u], xb[u], xa[u]));
+        }
+    }
+}
+
+template <int W, class F>
+int launch_broadcast_w(const F& f, const BroadcastPlan& plan, const float* a, const float* b,
+                       float* out, cudaStream_t stream) {
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+    static int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        int nb = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &nb, broadcast_kernel<W, F>, kEwThreads, 0);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        blocks_per_sm = nb > 0 ? nb : 1;
+    }
+    const int64_t tiles = ceil_div(plan.total_packs, kEwThreads * kEwUnroll);
+    const int grid = persistent_grid(info, blocks_per_sm, tiles);
+    broadcast_kernel<W, F><<<grid, kEwThreads, 0, stream>>>(f, plan, a, b, out);
+    return launch_status();
+}
+
+struct Dim {
+    int64_t size;
+    int64_t a;
+    int64_t b;
+};
+
+// Drops size-1 dimensions and merges neighbours that both operands walk contiguously
+// (or both broadcast), so [R, C] + [R, C] becomes 1-D and [N, R, C] + [1, 1, C] becomes 2-D.
+int collapse_dims(int ndim, const int64_t* shape, const int64_t* a_strides,
+                  const int64_t* b_strides, Dim* dims) {
+    int nd = 0;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] == 1) continue;
+        Dim d{shape[i], a_strides[i], b_strides[i]};
+        if (nd > 0) {
+            Dim& prev = dims[nd - 1];
+            if (prev.a == d.a * d.size && prev.b == d.b * d.size) {
+                prev.size *= d.size;
+                prev.a = d.a;
+                prev.b = d.b;
+                continue;
+            }
+        }
+        dims[nd++] = d;
+    }
+    if (nd == 0) {
+        dims[0] = Dim{1, 0, 0};
+        nd = 1;
+    }
+    return nd;
+}
+
+template <class F>
+int run_broadcast(const F& f, const float* a, const float* b, float* out, int ndim,
+                  const int64_t* shape, const int64_t* a_strides, const int64_t* b_strides,
+                  cudaStream_t stream) {
+    if (a == nullptr || b == nullptr || out == nullptr || shape == nullptr ||
+        a_strides == nullptr || b_strides == nullptr || ndim < 1 || ndim > 8) {
+        return FDL_ERR_INVALID_ARGUMENT;
+    }
+    int64_t total = 1;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] < 0 || a_strides[i] < 0 || b_strides[i] < 0) return FDL_ERR_INVALID_ARGUMENT;
+        total *= shape[i];
+    }
+    if (total == 0) return FDL_OK;
+
+    Dim dims[8];
+    const int nd = collapse_dims(ndim, shape, a_strides, b_strides, dims);
+    const Dim inner = dims[nd - 1];
+
+    // Fully contiguous operands: the plain streaming kernel does it with no index math.
+    if (nd == 1 && inner.a == 1 && inner.b == 1) {
+        return launch_map<2, F>(f, a, b, nullptr, out, total, stream);
+    }
+
+    // 128-bit path: innermost extent a multiple of 4, unit or zero inner strides, and
+    // every vector-loaded operand keeps 16-byte alignment across the outer dimensions.
+    bool vec = (inner.size % 4 == 0) && (inner.a == 0 || inner.a == 1) &&
+               (inner.b == 0 || inner.b == 1) && aligned16(out) &&
+               (inner.a == 0 || aligned16(a)) && (inner.b == 0 || aligned16(b));
+    for (int i = 0; i + 1 < nd && vec; ++i) {
+        if (inner.a == 1 && dims[i].a % 4 != 0) vec = false;
+        if (inner.b == 1 && dims[i].b % 4 != 0) vec = false;
+    }
+    const int w = vec ? 4 : 1;
+    const int64_t inner_packs = inner.size / w;
+    if (inner_packs >= (int64_t{1} << 31)) return FDL_ERR_UNSUPPORTED;
+
+    // Outer dimensions, innermost first.
+    BroadcastPlan plan{};
+    plan.inner_div = make_fastdiv(static_cast<uint32_t>(inner_packs));
+    plan.a_inner = inner.a;
+    plan.b_inner = inner.b;
+    plan.nouter = nd - 1;
+    int64_t outer_rows_below_top = 1;  // product of outer dims except the outermost
+    for (int k = 0; k < nd - 1; ++k) {
+        const Dim& d = dims[nd - 2 - k];
+        if (d.size >= (int64_t{1} << 31)) return FDL_ERR_UNSUPPORTED;
+        plan.outer_div[k] = make_fastdiv(static_cast<uint32_t>(d.size));
+        plan.a_outer[k] = d.a;
+        plan.b_outer[k] = d.b;
+        if (k + 1 < nd - 1) outer_rows_below_top *= d.size;
+    }
+
+    // The device index is 31-bit: walk the outermost dimension in slabs that fit.
+    constexpr int64_t kMaxPacks = (int64_t{1} << 31) - 1;
+    const int64_t packs_per_top = inner_packs * outer_rows_below_top;
+    if (packs_per_top > kMaxPacks) return FDL_ERR_UNSUPPORTED;
+    const int64_t top_size = nd >= 2 ? dims[0].size : 1;
+    const int64_t top_a = nd >= 2 ? dims[0].a : 0;
+    const int64_t top_b = nd >= 2 ? dims[0].b : 0;
+    const int64_t slab = kMaxPacks / packs_per_top;
+    for (int64_t start = 0; start < top_size; start += slab) {
+        const int64_t count = top_size - start < slab ? top_size - start : slab;
+        plan.total_packs = static_cast<uint32_t>(count * packs_per_top);
+        const float* a_s = a + start * top_a;
+        const float* b_s = b + start * top_b;
+        float* out_s = out + start * packs_per_top * w;
+        const int st = vec ? launch_broadcast_w<4, F>(f, plan, a_s, b_s, out_s, stream)
+                           : launch_broadcast_w<1, F>(f, plan, a_s, b_s, out_s, stream);
+        if (st != FDL_OK) return st;
+    }
+    return FDL_OK;
+}
+
+}  // namespace
+
+}  // namespace fdl
+
+using namespace fdl;
+
+extern "C" {
+
+int fdl_binary_f32(const float* a, const float* b, float* out, int64_t n, int op, void* stream) {
+    if (n < 0 || (n > 0 && (a == nullptr || b == nullptr || out == nullptr))) {
+        return FDL_ERR_INVALID_ARGUMENT;
+    }
+    cudaStream_t s = as_stream(stream);
+    switch (op) {
+        case FDL_ADD:
+            return launch_map<2>(AddFn{}, a, b, nullptr, out, n, s);
+        case FDL_SUB:
+            return launch_map<2>(SubFn{}, a, b, nullptr, out, n, s);
+        case FDL_MUL:
+            return launch_map<2>(MulFn{}, a, b, nullptr, out, n, s);
+        case FDL_DIV:
+            return launch_map<2>(DivFn{}, a, b, nullptr, out, n, s);
+        default:
+            return FDL_ERR_INVALID_ARGUMENT;
+    }
+}
+
+int fdl_unary_f32(const float* x, float* out, int64_t n, int op, float alpha, void* stream) {
+    if (n < 0 || (n > 0 && (x == nullptr || out == nullptr))) return FDL_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = as_stream(stream);
+    switch (op) {
+        case FDL_RELU:
+            return launch_map<1>(ReluFn{}, x, nullptr, nullptr, out, n, s);
+        case FDL_LEAKY_RELU:
+            return launch_map<1>(LeakyReluFn{alpha}, x, nullptr, nullptr, out, n, s);
+        case FDL_GELU:
+            return launch_map<1>(GeluFn{}, x, nullptr, nullptr, out, n, s);
+        case FDL_SIGMOID:
+            return launch_map<1>(SigmoidFn{}, x, nullptr, nullptr, out, n, s);
+        case FDL_TANH:
+            return launch_map<1>(TanhFn{}, x, nullptr, nullptr, out, n, s);
+        default:
+            return FDL_ERR_INVALID_ARGUMENT;
+    }
+}
+
+int fdl_mul_add_relu_f32(const float* a, const float* b, const float* c, float* out, int64_t n,
+                         void* stream) {
+    if (n < 0 || (n > 0 && (a == nullptr || b == nullptr || c == nullptr || out == nullptr))) {
+        return FDL_ERR_INVALID_ARGUMENT;
+    }
+    return launch_map<3>(MulAddReluFn{}, a, b, c, out, n, as_stream(stream));
+}
+
+int fdl_broadcast_binary_f32(const float* a, const float* b, float* out, int ndim,
+                             const int64_t* shape, const int64_t* a_strides,
+                             const int64_t* b_strides, int op, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    switch (op) {
+        case FDL_ADD:
+            return run_broadcast(AddFn{}, a, b, out, ndim, shape, a_strides, b_strides, s);
+        case FDL_SUB:
+            return run_broadcast(SubFn{}, a, b, out, ndim, shape, a_strides, b_strides, s);
+        case FDL_MUL:
+            return run_broadcast(MulFn{}, a, b, out, ndim, shape, a_strides, b_strides, s);
+        case FDL_DIV:
+            return run_broadcast(DivFn{}, a, b, out, ndim, shape, a_strides, b_strides, s);
+        default:
+            return FDL_ERR_INVALID_ARGUMENT;
+    }
+}
+
+int fdl_add_row_bias_f32(float* out, const float* bias, int64_t rows, int64_t cols,
+                         void* stream) {
+    if (rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
+    const int64_t shape[2] = {rows, cols};
+    const int64_t a_strides[2] = {cols, 1};
+    const int64_t b_strides[2] = {0, 1};
+    return run_broadcast(AddFn{}, out, bias, out, 2, shape, a_strides, b_strides,
+                         as_stream(stream));
+}
+
+int fdl_add_row_bias_relu_f32(float* out, const float* bias, int64_t rows, int64_t cols,
+                              void* stream) {
+    if (rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
+    const int64_t shape[2] = {rows, cols};
+    const int64_t a_strides[2] = {cols, 1};
+    const int64_t b_strides[2] = {0, 1};
+    return run_broadcast(AddReluFn{}, out, bias, out, 2, shape, a_strides, b_strides,
+                         as_stream(stream));
+}
+
+}  // extern "C"

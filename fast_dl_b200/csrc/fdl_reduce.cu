@@ -1,0 +1,755 @@
+// Reductions (fp32 in; fp32 / int64 out): the reference-order 1024-block tree, the
+// deterministic full sum, row-wise sum/mean/max/argmax and column-wise sum/mean/max.
+//
+// All of them read each input byte once with 128-bit loads and keep several independent
+// accumulators per thread; the combine tree is registers -> warp shuffles -> shared
+// memory -> distributed shared memory of a thread-block cluster -> (for grid-wide
+// results) per-cluster partials in scratch that the last cluster to finish folds in a
+// fixed order.  No floating-point atomics anywhere, so results are run-to-run identical.
+#include <cooperative_groups.h>
+
+#include <cfloat>
+#include <climits>
+#include <cmath>
+
+#include "fdl_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace fdl {
+
+namespace {
+
+// ======================================================================================
+// 1024-element block sums in the reference's pairing order
+// ======================================================================================
+//
+// The reference reduces each 1024-float block in shared memory, pairing d[i] += d[i+s]
+// with s = 512..1 ("address", src/kernels/cuda/reduction.cu:34-50) or d[i] += d[i+s] for
+// i % 2s == 0 with s = 1..512 ("interleave", :8-24).  Both are binary trees over the ten
+// bits of the element index: "address" folds bit 9 first and bit 0 last, "interleave"
+// the other way round.  Here one WARP owns a block.  Lane l loads float4 number
+// l + 32*r (r = 0..7), so an element's index bits are  [r:3][lane:5][component:2]:
+// folding r happens in registers, folding the lane bits is five shuffles, folding the
+// component bits is two adds.  Doing those three groups in the right order reproduces
+// either tree bit for bit (float addition is commutative, so which side of a pair a
+// value sits on does not matter).
+
+constexpr int kBlk = 1024;
+constexpr int kBlkThreads = 256;
+constexpr int kBlkWarps = kBlkThreads / kWarp;
+
+template <int TREE>
+__device__ __forceinline__ float fold_block_vec(const float4 (&q)[8]) {
+    if (TREE == FDL_TREE_ADDRESS) {
+        float c[4];
+        {
+            // bits 9, 8, 7 (register index r)
+            float4 a0, a1, a2, a3;
+            a0.x = q[0].x + q[4].x; a0.y = q[0].y + q[4].y; a0.z = q[0].z + q[4].z; a0.w = q[0].w + q[4].w;
+            a1.x = q[1].x + q[5].x; a1.y = q[1].y + q[5].y; a1.z = q[1].z + q[5].z; a1.w = q[1].w + q[5].w;
+            a2.x = q[2].x + q[6].x; a2.y = q[2].y + q[6].y; a2.z = q[2].z + q[6].z; a2.w = q[2].w + q[6].w;
+            a3.x = q[3].x + q[7].x; a3.y = q[3].y + q[7].y; a3.z = q[3].z + q[7].z; a3.w = q[3].w + q[7].w;
+            a0.x += a2.x; a0.y += a2.y; a0.z += a2.z; a0.w += a2.w;
+            a1.x += a3.x; a1.y += a3.y; a1.z += a3.z; a1.w += a3.w;
+            c[0] = a0.x + a1.x; c[1] = a0.y + a1.y; c[2] = a0.z + a1.z; c[3] = a0.w + a1.w;
+        }
+        // bits 6..2 (lane bits 4..0)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) c[k] += __shfl_xor_sync(kFullMask, c[k], o);
+        }
+        // bits 1, 0 (component)
+        c[0] += c[2];
+        c[1] += c[3];
+        return c[0] + c[1];
+    } else {
+        float w[8];
+        // bits 0, 1 (component)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) w[r] = (q[r].x + q[r].y) + (q[r].z + q[r].w);
+        // bits 2..6 (lane bits 0..4)
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) w[r] += __shfl_xor_sync(kFullMask, w[r], o);
+        }
+        // bits 7, 8, 9 (register index)
+        w[0] += w[1]; w[2] += w[3]; w[4] += w[5]; w[6] += w[7];
+        w[0] += w[2]; w[4] += w[6];
+        return w[0] + w[4];
+    }
+}
+
+// Scalar-load variant for inputs that are not 16-byte aligned: lane l holds elements
+// l + 32*r (r = 0..31), i.e. index bits [r:5][lane:5].
+template <int TREE>
+__device__ __forceinline__ float fold_block_scalar(float (&e)[32]) {
+    if (TREE == FDL_TREE_ADDRESS) {
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+            for (int r = 0; r < s; ++r) e[r] += e[r + s];
+        }
+        float v = e[0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+        return v;
+    } else {
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+            for (int r = 0; r < 32; ++r) e[r] += __shfl_xor_sync(kFullMask, e[r], o);
+        }
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+            for (int r = 0; r < 32; r += 2 * s) e[r] += e[r + s];
+        }
+        return e[0];
+    }
+}
+
+template <int TREE, bool VEC>
+__global__ void __launch_bounds__(kBlkThreads)
+block_reduce_1024_kernel(const float* x, float* out, int64_t nblocks) {
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    for (int64_t blk = static_cast<int64_t>(blockIdx.x) * kBlkWarps + warp; blk < nblocks;
+         blk += static_cast<int64_t>(gridDim.x) * kBlkWarps) {
+        const float* src = x + blk * kBlk;
+        float r;
+        if (VEC) {
+            float4 q[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i] = ld_stream(reinterpret_cast<const float4*>(src) + lane + 32 * i);
+            r = fold_block_vec<TREE>(q);
+        } else {
+            float e[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) e[i] = ld_stream(src + lane + 32 * i);
+            r = fold_block_scalar<TREE>(e);
+        }
+        if (lane == 0) out[blk] = r;
+    }
+}
+
+// ======================================================================================
+// Shared pieces of the grid-wide reductions
+// ======================================================================================
+
+constexpr int kSumThreads = 512;
+constexpr int kSumUnroll = 4;
+constexpr int kSumCluster = 4;  // CTAs per cluster; partials are folded through DSMEM
+constexpr int kCounterBytes = 256;
+
+// Block-wide sum in double; result valid in thread 0.  `red` holds one slot per warp.
+template <int THREADS>
+__device__ __forceinline__ double block_sum_double(double v, double* red) {
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double total = 0.0;
+    if (warp == 0) {
+        double t = lane < THREADS / kWarp ? red[lane] : 0.0;
+        total = warp_sum(t);
+    }
+    __syncthreads();
+    return total;
+}
+
+// ======================================================================================
+// Full sum
+// ======================================================================================
+//
+// Scratch layout: [0,256): uint32 arrival counter (zero between launches);
+// [256, ...): one double per cluster.
+
+__global__ void __launch_bounds__(kSumThreads)
+sum_kernel(const float* x, int64_t n, int64_t nvec, bool vec, float* out_f32, double* out_f64,
+           unsigned int* counter, double* partials) {
+    __shared__ double red[kSumThreads / kWarp];
+    __shared__ double cluster_slots[kSumCluster];
+    __shared__ bool is_last;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    // Arrive now, wait just before the first remote shared-memory access: by then every
+    // CTA of the cluster is known to be running, which DSMEM stores require.
+    cluster.barrier_arrive();
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * kSumThreads + threadIdx.x;
+    const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kSumThreads;
+
+    float acc = 0.0f;
+    if (vec) {
+        const float4* xv = reinterpret_cast<const float4*>(x);
+        float4 a[kSumUnroll];
+#pragma unroll
+        for (int u = 0; u < kSumUnroll; ++u) a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        int64_t i = tid;
+        for (; i + (kSumUnroll - 1) * nthreads < nvec; i += kSumUnroll * nthreads) {
+            float4 v[kSumUnroll];
+#pragma unroll
+            for (int u = 0; u < kSumUnroll; ++u) v[u] = ld_stream(xv + i + u * nthreads);
+#pragma unroll
+            for (int u = 0; u < kSumUnroll; ++u) {
+                a[u].x += v[u].x; a[u].y += v[u].y; a[u].z += v[u].z; a[u].w += v[u].w;
+            }
+        }
+        for (; i < nvec; i += nthreads) {
+            const float4 v = ld_stream(xv + i);
+            a[0].x += v.x; a[0].y += v.y; a[0].z += v.z; a[0].w += v.w;
+        }
+        float s[kSumUnroll];
+#pragma unroll
+        for (int u = 0; u < kSumUnroll; ++u) s[u] = (a[u].x + a[u].y) + (a[u].z + a[u].w);
+        acc = (s[0] + s[1]) + (s[2] + s[3]);
+        for (int64_t j = nvec * 4 + tid; j < n; j += nthreads) acc += x[j];
+    } else {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int64_t i = tid;
+        for (; i + 3 * nthreads < n; i += 4 * nthreads) {
+            const float v0 = ld_stream(x + i), v1 = ld_stream(x + i + nthreads);
+            const float v2 = ld_stream(x + i + 2 * nthreads), v3 = ld_stream(x + i + 3 * nthreads);
+            a0 += v0; a1 += v1; a2 += v2; a3 += v3;
+        }
+        for (; i < n; i += nthreads) a0 += ld_stream(x + i);
+        acc = (a0 + a1) + (a2 + a3);
+    }
+
+    const double block_total = block_sum_double<kSumThreads>(static_cast<double>(acc), red);
+
+    // Cluster stage: every CTA drops its partial into the leader's shared memory.
+    const unsigned int rank = cluster.block_rank();
+    cluster.barrier_wait();
+    if (threadIdx.x == 0) {
+        double* leader_slots = cluster.map_shared_rank(cluster_slots, 0);
+        leader_slots[rank] = block_total;
+    }
+    cluster.sync();
+    if (rank != 0) return;
+
+    const unsigned int nclusters = gridDim.x / kSumCluster;
+    const unsigned int cluster_id = blockIdx.x / kSumCluster;
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll
+        for (int k = 0; k < kSumCluster; ++k) t += cluster_slots[k];
+        partials[cluster_id] = t;
+        __threadfence();
+        const unsigned int ticket = atomicAdd(counter, 1u);
+        is_last = (ticket == nclusters - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+
+    // The last cluster leader folds all partials in index order.
+    __threadfence();
+    double t = 0.0;
+    for (unsigned int k = threadIdx.x; k < nclusters; k += kSumThreads) t += __ldcg(partials + k);
+    const double total = block_sum_double<kSumThreads>(t, red);
+    if (threadIdx.x == 0) {
+        if (out_f32 != nullptr) *out_f32 = static_cast<float>(total);
+        if (out_f64 != nullptr) *out_f64 = total;
+        *counter = 0;  // ready for the next launch
+    }
+}
+
+int sum_grid(const DeviceInfo* info, int* grid_out) {
+    static int clusters = 0;
+    if (clusters == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kSumCluster * 64);
+        cfg.blockDim = dim3(kSumThreads);
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = kSumCluster;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, sum_kernel, &cfg);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        clusters = n > 0 ? n : 1;
+    }
+    (void)info;
+    *grid_out = clusters * kSumCluster;
+    return FDL_OK;
+}
+
+// ======================================================================================
+// Row-wise reductions (axis 1 of a row-major matrix)
+// ======================================================================================
+
+struct SumRed {
+    using State = float;
+    using Out = float;
+    __device__ static State identity() { return 0.0f; }
+    __device__ static State lift(float v, int) { return v; }
+    __device__ static State combine(State a, State b) { return a + b; }
+    __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    __device__ static Out finish(State a, int64_t, float) { return a; }
+};
+struct MeanRed : SumRed {
+    __device__ static Out finish(State a, int64_t, float divisor) { return a / divisor; }
+};
+struct MaxRed {
+    using State = float;
+    using Out = float;
+    __device__ static State identity() { return -INFINITY; }
+    __device__ static State lift(float v, int) { return v; }
+    __device__ static State combine(State a, State b) { return fmaxf(a, b); }
+    __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    __device__ static Out finish(State a, int64_t, float) { return a; }
+};
+struct ArgState {
+    float v;
+    int i;
+};
+struct ArgmaxRed {
+    using State = ArgState;
+    using Out = int64_t;
+    __device__ static State identity() { return ArgState{-INFINITY, INT_MAX}; }
+    __device__ static State lift(float v, int col) {
+        return ArgState{v != v ? -INFINITY : v, col};  // NaN ranks as -inf
+    }
+    __device__ static State combine(State a, State b) {
+        const bool take_b = (b.v > a.v) || (b.v == a.v && b.i < a.i);
+        return take_b ? b : a;
+    }
+    __device__ static State shuffle_xor(State a, int o) {
+        return ArgState{__shfl_xor_sync(kFullMask, a.v, o), __shfl_xor_sync(kFullMask, a.i, o)};
+    }
+    __device__ static Out finish(State a, int64_t, float) {
+        return a.i == INT_MAX ? 0 : static_cast<int64_t>(a.i);
+    }
+};
+
+constexpr int kRowThreads = 256;
+constexpr int kRowUnroll = 4;
+
+// TPR threads cooperate on a row (32: one warp per row, 8 rows per CTA; 256: one CTA per
+// row).  W = 4 needs cols % 4 == 0 and a 16-byte aligned base.
+template <class R, int TPR, int W>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out, float divisor) {
+    using State = typename R::State;
+    constexpr int kRowsPerCta = kRowThreads / TPR;
+    __shared__ State red[kRowThreads / kWarp];
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    const int t = threadIdx.x % TPR;        // position inside the row team
+    const int team = threadIdx.x / TPR;
+    const int npack = cols / W;
+
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + team; row < rows;
+         row += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+        const float* xr = x + row * cols;
+        State acc[kRowUnroll];
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
+        int p = t;
+        if (W == 4) {
+            const float4* xv = reinterpret_cast<const float4*>(xr);
+            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
+                float4 v[kRowUnroll];
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * TPR);
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) {
+                    const int c = (p + u * TPR) * 4;
+                    acc[u] = R::combine(acc[u], R::lift(v[u].x, c));
+                    acc[u] = R::combine(acc[u], R::lift(v[u].y, c + 1));
+                    acc[u] = R::combine(acc[u], R::lift(v[u].z, c + 2));
+                    acc[u] = R::combine(acc[u], R::lift(v[u].w, c + 3));
+                }
+            }
+            for (; p < npack; p += TPR) {
+                const float4 v = ld_stream(xv + p);
+                const int c = p * 4;
+                acc[0] = R::combine(acc[0], R::lift(v.x, c));
+                acc[0] = R::combine(acc[0], R::lift(v.y, c + 1));
+                acc[0] = R::combine(acc[0], R::lift(v.z, c + 2));
+                acc[0] = R::combine(acc[0], R::lift(v.w, c + 3));
+            }
+        } else {
+            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
+                float v[kRowUnroll];
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xr + p + u * TPR);
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) {
+                    acc[u] = R::combine(acc[u], R::lift(v[u], p + u * TPR));
+                }
+            }
+            for (; p < npack; p += TPR) acc[0] = R::combine(acc[0], R::lift(ld_stream(xr + p), p));
+        }
+        State s = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+#pragma unroll
+        for (int o = kWarp / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
+        if (TPR == kWarp) {
+            if (lane == 0) out[row] = R::finish(s, cols, divisor);
+        } else {
+            // One CTA per row: every thread of the CTA runs the same trip count.
+            if (lane == 0) red[warp] = s;
+            __syncthreads();
+            if (warp == 0) {
+                State z = lane < kRowThreads / kWarp ? red[lane] : R::identity();
+#pragma unroll
+                for (int o = kWarp / 2; o > 0; o >>= 1) z = R::combine(z, R::shuffle_xor(z, o));
+                if (lane == 0) out[row] = R::finish(z, cols, divisor);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+template <class R, int TPR, int W>
+int launch_rows_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
+                    cudaStream_t stream) {
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+    constexpr int kRowsPerCta = kRowThreads / TPR;
+    const int grid = persistent_grid(info, 8, ceil_div(rows, kRowsPerCta));
+    reduce_rows_kernel<R, TPR, W><<<grid, kRowThreads, 0, stream>>>(
+        x, rows, static_cast<int>(cols), out, static_cast<float>(cols));
+    return launch_status();
+}
+
+template <class R>
+int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
+                cudaStream_t stream) {
+    if (rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
+    if (rows == 0) return FDL_OK;
+    if (x == nullptr || out == nullptr || cols == 0) return FDL_ERR_INVALID_ARGUMENT;
+    if (cols >= INT_MAX) return FDL_ERR_UNSUPPORTED;
+    const bool vec = aligned16(x) && cols % 4 == 0;
+    const bool wide = cols >= 2048;  // a whole CTA per row once a warp would loop too long
+    if (vec) {
+        return wide ? launch_rows_cfg<R, kRowThreads, 4>(x, rows, cols, out, stream)
+                    : launch_rows_cfg<R, kWarp, 4>(x, rows, cols, out, stream);
+    }
+    return wide ? launch_rows_cfg<R, kRowThreads, 1>(x, rows, cols, out, stream)
+                : launch_rows_cfg<R, kWarp, 1>(x, rows, cols, out, stream);
+}
+
+// ======================================================================================
+// Column-wise reductions (axis 0 of `batch` stacked row-major [rows, cols] matrices)
+// ======================================================================================
+//
+// Threads own columns (4 adjacent ones each on the vector path) and march down the rows,
+// so every warp-level load is one contiguous 512-byte run.  A CTA is TX threads wide and
+// TY = 256/TX rows deep; gridDim.y slices the rows into chunks.  The TY partial rows are
+// folded in shared memory; chunk partials go to scratch and the last chunk to arrive for
+// a column block folds them in chunk order.
+//
+// Scratch layout: [0, 4*ncounters) counters padded to 256 B, then
+// float partials[chunks][batch][cols].
+
+constexpr int kColThreads = 256;
+
+struct ColSum {
+    __device__ static float identity() { return 0.0f; }
+    __device__ static float combine(float a, float b) { return a + b; }
+};
+struct ColMax {
+    __device__ static float identity() { return -INFINITY; }
+    __device__ static float combine(float a, float b) { return fmaxf(a, b); }
+};
+
+template <class R, int W>
+__global__ void __launch_bounds__(kColThreads)
+reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float* partials,
+                   unsigned int* counters, int tx, int rows_per_chunk, float scale) {
+    extern __shared__ float tile[];  // [TY][TX*W]
+    __shared__ bool is_last;
+    const int ty_count = kColThreads / tx;
+    const int cx = threadIdx.x % tx;
+    const int ry = threadIdx.x / tx;
+    const int64_t col = (static_cast<int64_t>(blockIdx.x) * tx + cx) * W;
+    const int chunk = blockIdx.y;
+    const int nchunks = gridDim.y;
+    const int64_t b = blockIdx.z;
+    const float* xb = x + b * rows * cols;
+
+    float acc[2][W];
+#pragma unroll
+    for (int k = 0; k < W; ++k) acc[0][k] = acc[1][k] = R::identity();
+
+    const int64_t r_begin = static_cast<int64_t>(chunk) * rows_per_chunk;
+    int64_t r_end = r_begin + rows_per_chunk;
+    if (r_end > rows) r_end = rows;
+    if (col < cols) {
+        int64_t r = r_begin + ry;
+        // Two rows in flight per thread.
+        for (; r + ty_count < r_end; r += 2 * ty_count) {
+            if (W == 4) {
+                const float4 v0 = ld_stream(reinterpret_cast<const float4*>(xb + r * cols + col));
+                const float4 v1 =
+                    ld_stream(reinterpret_cast<const float4*>(xb + (r + ty_count) * cols + col));
+                acc[0][0] = R::combine(acc[0][0], v0.x); acc[0][1 % W] = R::combine(acc[0][1 % W], v0.y);
+                acc[0][2 % W] = R::combine(acc[0][2 % W], v0.z); acc[0][3 % W] = R::combine(acc[0][3 % W], v0.w);
+                acc[1][0] = R::combine(acc[1][0], v1.x); acc[1][1 % W] = R::combine(acc[1][1 % W], v1.y);
+                acc[1][2 % W] = R::combine(acc[1][2 % W], v1.z); acc[1][3 % W] = R::combine(acc[1][3 % W], v1.w);
+            } else {
+                acc[0][0] = R::combine(acc[0][0], ld_stream(xb + r * cols + col));
+                acc[1][0] = R::combine(acc[1][0], ld_stream(xb + (r + ty_count) * cols + col));
+            }
+        }
+        for (; r < r_end; r += ty_count) {
+            if (W == 4) {
+                const float4 v0 = ld_stream(reinterpret_cast<const float4*>(xb + r * cols + col));
+                acc[0][0] = R::combine(acc[0][0], v0.x); acc[0][1 % W] = R::combine(acc[0][1 % W], v0.y);
+                acc[0][2 % W] = R::combine(acc[0][2 % W], v0.z); acc[0][3 % W] = R::combine(acc[0][3 % W], v0.w);
+            } else {
+                acc[0][0] = R::combine(acc[0][0], ld_stream(xb + r * cols + col));
+            }
+        }
+    }
+    const int tile_w = tx * W;
+#pragma unroll
+    for (int k = 0; k < W; ++k) tile[ry * tile_w + cx * W + k] = R::combine(acc[0][k], acc[1][k]);
+    __syncthreads();
+
+    // Fold the TY rows of the tile (fixed order) -- threads 0..tile_w-1 own one column each.
+    float* dst = nchunks == 1 ? out + b * cols
+                              : partials + (static_cast<int64_t>(chunk) * gridDim.z + b) * cols;
+    const int64_t col0 = static_cast<int64_t>(blockIdx.x) * tile_w;
+    for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
+        float s = tile[c];
+        for (int y = 1; y < ty_count; ++y) s = R::combine(s, tile[y * tile_w + c]);
+        if (col0 + c < cols) dst[col0 + c] = nchunks == 1 ? s * scale : s;
+    }
+    if (nchunks == 1) return;
+
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* ctr = counters + b * gridDim.x + blockIdx.x;
+        const unsigned int ticket = atomicAdd(ctr, 1u);
+        is_last = ticket == static_cast<unsigned int>(nchunks - 1);
+        if (is_last) *ctr = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
+        if (col0 + c >= cols) continue;
+        float s = R::identity();
+        for (int k = 0; k < nchunks; ++k) {
+            s = R::combine(s, __ldcg(partials + (static_cast<int64_t>(k) * gridDim.z + b) * cols + col0 + c));
+        }
+        out[b * cols + col0 + c] = s * scale;
+    }
+}
+
+struct ColsGeometry {
+    int tx;              // threads across columns (power of two, <= 256)
+    int w;               // floats per thread (4 or 1)
+    int col_blocks;      // gridDim.x
+    int chunks;          // gridDim.y
+    int rows_per_chunk;
+    size_t counter_bytes;
+    size_t scratch_bytes;
+};
+
+int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool vec,
+                  ColsGeometry* g) {
+    g->w = vec ? 4 : 1;
+    const int64_t packs = ceil_div(cols, g->w);
+    int tx = 1;
+    while (tx < 64 && tx < packs) tx <<= 1;  // up to 64 threads = 1 KiB of a row per CTA
+    g->tx = tx;
+    g->col_blocks = static_cast<int>(ceil_div(packs, tx));
+    const int ty = kColThreads / tx;
+    // Aim for ~8 CTAs per SM, but keep at least 4 rows per thread in a chunk.
+    const int64_t target = static_cast<int64_t>(sm_count) * 8;
+    int64_t chunks = ceil_div(target, static_cast<int64_t>(g->col_blocks) * batch);
+    const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 4);
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 65535) chunks = 65535;
+    g->rows_per_chunk = static_cast<int>(ceil_div(rows, chunks));
+    g->chunks = static_cast<int>(ceil_div(rows, g->rows_per_chunk));
+    const size_t ncounters = static_cast<size_t>(g->col_blocks) * batch;
+    g->counter_bytes = ((ncounters * sizeof(unsigned int) + 255) / 256) * 256;
+    g->scratch_bytes =
+        g->chunks == 1
+            ? 0
+            : g->counter_bytes +
+                  ((static_cast<size_t>(g->chunks) * batch * cols * sizeof(float) + 255) / 256) * 256;
+    return FDL_OK;
+}
+
+// The SM count enters the geometry, so the scratch query needs a device too; without
+// one (a build-only machine) it assumes the 148 SMs of a B200.
+int sm_count_or_default() {
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) {
+        cudaGetLastError();
+        return 148;
+    }
+    return info->sm_count;
+}
+
+}  // namespace
+
+}  // namespace fdl
+
+using namespace fdl;
+
+extern "C" {
+
+int fdl_block_reduce_1024_f32(const float* x, float* out, int64_t n, int tree, void* stream) {
+    if (n < 0) return FDL_ERR_INVALID_ARGUMENT;
+    const int64_t nblocks = n / kBlk;
+    if (nblocks == 0) return FDL_OK;
+    if (x == nullptr || out == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    if (tree != FDL_TREE_INTERLEAVE && tree != FDL_TREE_ADDRESS) return FDL_ERR_INVALID_ARGUMENT;
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+    const int grid = persistent_grid(info, 8, ceil_div(nblocks, kBlkWarps));
+    cudaStream_t s = as_stream(stream);
+    const bool vec = aligned16(x);
+    if (tree == FDL_TREE_ADDRESS) {
+        if (vec) block_reduce_1024_kernel<FDL_TREE_ADDRESS, true><<<grid, kBlkThreads, 0, s>>>(x, out, nblocks);
+        else block_reduce_1024_kernel<FDL_TREE_ADDRESS, false><<<grid, kBlkThreads, 0, s>>>(x, out, nblocks);
+    } else {
+        if (vec) block_reduce_1024_kernel<FDL_TREE_INTERLEAVE, true><<<grid, kBlkThreads, 0, s>>>(x, out, nblocks);
+        else block_reduce_1024_kernel<FDL_TREE_INTERLEAVE, false><<<grid, kBlkThreads, 0, s>>>(x, out, nblocks);
+    }
+    return launch_status();
+}
+
+size_t fdl_sum_scratch_bytes(int64_t n) {
+    (void)n;
+    // One double per cluster; the cluster count is bounded by SMs * resident CTAs.
+    return kCounterBytes + 4096 * sizeof(double);
+}
+
+int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* scratch,
+                size_t scratch_bytes, void* stream) {
+    if (n < 0 || (out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
+    if (n > 0 && x == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+    const size_t need = fdl_sum_scratch_bytes(n);
+    if (scratch == nullptr) {
+        status = get_workspace(need, &scratch);
+        if (status != FDL_OK) return status;
+    } else if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) {
+        return FDL_ERR_WORKSPACE;
+    }
+    int grid = 0;
+    status = sum_grid(info, &grid);
+    if (status != FDL_OK) return status;
+    // Small inputs do not need the whole machine: one cluster per 64 KiB, at least one.
+    const int64_t want = ceil_div(n, int64_t{16384} * kSumCluster) * kSumCluster;
+    if (want < grid) grid = want < kSumCluster ? kSumCluster : static_cast<int>(want);
+    if (grid / kSumCluster > 4096) grid = 4096 * kSumCluster;
+
+    const bool vec = aligned16(x);
+    const int64_t nvec = vec ? n / 4 : 0;
+    unsigned int* counter = static_cast<unsigned int*>(scratch);
+    double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kSumThreads);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = kSumCluster;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sum_kernel, x, n, nvec, vec, out_f32, out_f64,
+                                       counter, partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_status();
+}
+
+int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,
+                        void* stream) {
+    cudaStream_t s = as_stream(stream);
+    switch (op) {
+        case FDL_REDUCE_SUM:
+            return launch_rows<SumRed>(x, rows, cols, out, s);
+        case FDL_REDUCE_MEAN:
+            return launch_rows<MeanRed>(x, rows, cols, out, s);
+        case FDL_REDUCE_MAX:
+            return launch_rows<MaxRed>(x, rows, cols, out, s);
+        default:
+            return FDL_ERR_INVALID_ARGUMENT;
+    }
+}
+
+int fdl_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, int64_t* out, void* stream) {
+    return launch_rows<ArgmaxRed>(x, rows, cols, out, as_stream(stream));
+}
+
+size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols) {
+    if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+    // Whether the 128-bit path is taken depends on pointer alignment too: report the
+    // larger of the two geometries.
+    const int sms = sm_count_or_default();
+    ColsGeometry gv, gs;
+    cols_geometry(sms, batch, rows, cols, cols % 4 == 0, &gv);
+    cols_geometry(sms, batch, rows, cols, false, &gs);
+    return gv.scratch_bytes > gs.scratch_bytes ? gv.scratch_bytes : gs.scratch_bytes;
+}
+
+int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out,
+                        int op, double mean_divisor, void* scratch, size_t scratch_bytes,
+                        void* stream) {
+    if (batch < 0 || rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
+    if (batch == 0 || cols == 0) return FDL_OK;
+    if (x == nullptr || out == nullptr || rows == 0) return FDL_ERR_INVALID_ARGUMENT;
+    if (op != FDL_REDUCE_SUM && op != FDL_REDUCE_MEAN && op != FDL_REDUCE_MAX) {
+        return FDL_ERR_INVALID_ARGUMENT;
+    }
+    if (op == FDL_REDUCE_MEAN && !(mean_divisor > 0.0)) return FDL_ERR_INVALID_ARGUMENT;
+    if (batch > 65535) return FDL_ERR_UNSUPPORTED;
+    int status = FDL_OK;
+    const DeviceInfo* info = current_device_info(&status);
+    if (info == nullptr) return status;
+
+    const bool vec = aligned16(x) && cols % 4 == 0;
+    ColsGeometry g;
+    cols_geometry(info->sm_count, batch, rows, cols, vec, &g);
+    float* partials = nullptr;
+    unsigned int* counters = nullptr;
+    if (g.chunks > 1) {
+        if (scratch == nullptr) {
+            status = get_workspace(g.scratch_bytes, &scratch);
+            if (status != FDL_OK) return status;
+        } else if (scratch_bytes < g.scratch_bytes ||
+                   (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) {
+            return FDL_ERR_WORKSPACE;
+        }
+        counters = static_cast<unsigned int*>(scratch);
+        partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + g.counter_bytes);
+    }
+    const float scale = op == FDL_REDUCE_MEAN ? static_cast<float>(1.0 / mean_divisor) : 1.0f;
+    const dim3 grid(g.col_blocks, g.chunks, static_cast<unsigned int>(batch));
+    const size_t smem = static_cast<size_t>(kColThreads) * g.w * sizeof(float);
+    cudaStream_t s = as_stream(stream);
+    if (op == FDL_REDUCE_MAX) {
+        if (vec) reduce_cols_kernel<ColMax, 4><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
+        else reduce_cols_kernel<ColMax, 1><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
+    } else {
+        if (vec) reduce_cols_kernel<ColSum, 4><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
+        else reduce_cols_kernel<ColSum, 1><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
+    }
+    return launch_status();
+}
+
+}  // extern "C"

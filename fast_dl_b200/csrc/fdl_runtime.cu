@@ -1,0 +1,127 @@
+// Runtime plumbing of the C ABI: device selection, error text, cached device
+// properties and the library-owned per-device workspace.
+#include <mutex>
+
+#include "fdl_common.cuh"
+
+namespace fdl {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+std::mutex g_mutex;
+DeviceInfo g_info[kMaxDevices];
+bool g_info_valid[kMaxDevices] = {};
+
+struct Workspace {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+Workspace g_workspace[kMaxDevices];
+
+}  // namespace
+
+const DeviceInfo* current_device_info(int* status) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        *status = static_cast<int>(e);
+        return nullptr;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        *status = FDL_ERR_NO_DEVICE;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_info_valid[dev]) {
+        DeviceInfo info;
+        info.device = dev;
+        e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) {
+            e = cudaDeviceGetAttribute(&info.max_smem_optin,
+                                       cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        }
+        if (e != cudaSuccess) {
+            *status = static_cast<int>(e);
+            return nullptr;
+        }
+        g_info[dev] = info;
+        g_info_valid[dev] = true;
+    }
+    *status = FDL_OK;
+    return &g_info[dev];
+}
+
+int get_workspace(size_t bytes, void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return FDL_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Workspace& ws = g_workspace[dev];
+    if (ws.bytes < bytes) {
+        // Growing is rare (sizes depend on the SM count, not on the tensor), and the old
+        // block may still be in use by an enqueued kernel: wait for the device first.
+        if (ws.ptr != nullptr) {
+            e = cudaDeviceSynchronize();
+            if (e != cudaSuccess) return static_cast<int>(e);
+            cudaFree(ws.ptr);
+            ws.ptr = nullptr;
+            ws.bytes = 0;
+        }
+        size_t want = bytes < (size_t{1} << 20) ? (size_t{1} << 20) : bytes;
+        e = cudaMalloc(&ws.ptr, want);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        e = cudaMemset(ws.ptr, 0, want);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        ws.bytes = want;
+    }
+    *out = ws.ptr;
+    return FDL_OK;
+}
+
+}  // namespace fdl
+
+extern "C" {
+
+int fdl_version(void) { return 1000; }
+
+const char* fdl_error_string(int status) {
+    switch (status) {
+        case FDL_OK:
+            return "success";
+        case FDL_ERR_INVALID_ARGUMENT:
+            return "fdl: invalid argument";
+        case FDL_ERR_UNSUPPORTED:
+            return "fdl: unsupported shape or configuration";
+        case FDL_ERR_WORKSPACE:
+            return "fdl: scratch buffer too small or misaligned";
+        case FDL_ERR_DEVICE_WAIT:
+            return "fdl: a bounded device-side wait ran out";
+        case FDL_ERR_NO_DEVICE:
+            return "fdl: no usable CUDA device";
+        default:
+            break;
+    }
+    if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+    return "fdl: unknown status";
+}
+
+int fdl_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return FDL_ERR_NO_DEVICE;
+    }
+    return n;
+}
+
+int fdl_set_device(int device) { return static_cast<int>(cudaSetDevice(device)); }
+
+int fdl_stream_synchronize(void* stream) {
+    return static_cast<int>(cudaStreamSynchronize(fdl::as_stream(stream)));
+}
+
+}  // extern "C"

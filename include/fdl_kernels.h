@@ -1,0 +1,208 @@
+/*
+ * fdl_kernels.h -- C ABI of the sm_100a kernel library (libfdl_kernels.so).
+ *
+ * This is the drop-in boundary for fast_dl's bandwidth-bound tensor path.  Every
+ * entry point replaces (or extends in the same style) one host-callable function of
+ * the reference's kernel library; the reference location is cited above each
+ * declaration as <file>:<lines>, relative to the fast_dl source tree.
+ *
+ * Conventions shared by all entry points
+ *   - Plain pointers and sizes only; nothing here depends on PyTorch or C++.
+ *   - All data pointers are DEVICE pointers of the current device unless a name
+ *     starts with `h_` (host pointers, only in the fdl_host_* family).
+ *   - `stream` is a cudaStream_t passed as void*; NULL selects the legacy default
+ *     stream, which is what the reference launches on.
+ *   - The caller selects the device beforehand (fdl_set_device or cudaSetDevice in
+ *     the same CUDA runtime), exactly as the reference's ops do before calling
+ *     dl::kernels::*.
+ *   - Return value: 0 (FDL_OK) on success; a positive value is a cudaError_t from
+ *     the launch; a negative value is one of the FDL_ERR_* codes below.  Nothing
+ *     throws and nothing falls back to a CPU path.
+ *   - Launches are asynchronous with respect to the host, like the reference's.
+ *   - Element counts are int64_t.  The reference takes `int`/`size_t`; the C++
+ *     shims in dl::kernels keep those narrower types and widen here.
+ */
+#ifndef FDL_KERNELS_H_
+#define FDL_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDL_OK 0
+#define FDL_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, bad enum          */
+#define FDL_ERR_UNSUPPORTED (-2)      /* shape outside what the entry point implements   */
+#define FDL_ERR_WORKSPACE (-3)        /* caller-provided scratch too small or misaligned */
+#define FDL_ERR_DEVICE_WAIT (-4)      /* a bounded device-side wait ran out              */
+#define FDL_ERR_NO_DEVICE (-5)        /* no usable CUDA device / driver                  */
+
+/* Binary operator selector; numeric values equal dl::kernels::ElementwiseOp
+ * (include/dl/kernels/elementwise.hpp:7-12). */
+enum fdl_binary_op { FDL_ADD = 0, FDL_SUB = 1, FDL_MUL = 2, FDL_DIV = 3 };
+
+/* Unary operator selector; numeric values equal dl::kernels::ActivationOp
+ * (include/dl/kernels/activation.hpp:7-13). */
+enum fdl_unary_op {
+    FDL_RELU = 0,
+    FDL_LEAKY_RELU = 1,
+    FDL_GELU = 2,
+    FDL_SIGMOID = 3,
+    FDL_TANH = 4
+};
+
+/* Reduction selector for the axis reductions (no counterpart enum in the reference,
+ * which has no axis reductions). */
+enum fdl_reduce_op { FDL_REDUCE_SUM = 0, FDL_REDUCE_MEAN = 1, FDL_REDUCE_MAX = 2 };
+
+/* Tree order selector; numeric values equal dl::kernels::ReductionAlgo
+ * (include/dl/kernels/reduction.hpp:7-10). */
+enum fdl_block_tree { FDL_TREE_INTERLEAVE = 0, FDL_TREE_ADDRESS = 1 };
+
+/* ---- runtime -------------------------------------------------------------------- */
+
+/* Library ABI version: major*1000 + minor. */
+int fdl_version(void);
+
+/* Human-readable text for any value returned by this library (FDL_ERR_* or a
+ * cudaError_t).  Never NULL.  Plays the role of the message half of
+ * dl::cuda::check (src/core/CudaUtils.cpp:8-13). */
+const char* fdl_error_string(int status);
+
+/* Number of visible CUDA devices, or a negative FDL_ERR_* code. */
+int fdl_device_count(void);
+
+/* Make `device` current for the calling thread in the library's CUDA runtime.
+ * Replaces the cudaSetDevice call the reference's ops make before each kernel
+ * (e.g. src/ops/Elementwise.cpp:41). */
+int fdl_set_device(int device);
+
+/* Block the host until `stream` has drained. */
+int fdl_stream_synchronize(void* stream);
+
+/* Kernels that wait on the copy engine bound every wait; one that gives up raises a
+ * flag in host-visible memory instead of spinning.  This returns FDL_ERR_DEVICE_WAIT if
+ * the flag was raised since the last call (and clears it), else FDL_OK.  Meaningful
+ * after the stream has been synchronised. */
+int fdl_take_device_error(void);
+
+/* ---- elementwise ------------------------------------------------------------------ */
+
+/* out[i] = a[i] (op) b[i], i in [0,n).  IEEE round-to-nearest for all four operators;
+ * `out` may alias `a` or `b` exactly.  Replaces dl::kernels::elementwise
+ * (include/dl/kernels/elementwise.hpp:16, src/kernels/cuda/elementwise.cu:5-31,51-54)
+ * and, with op = FDL_ADD, dl::kernels::vector_add
+ * (include/dl/kernels/vector_add.hpp:13-14, src/kernels/cuda/vector_add.cu:7-21,35-42). */
+int fdl_binary_f32(const float* a, const float* b, float* out, int64_t n, int op,
+                   void* stream);
+
+/* out[i] = f(x[i]).  `alpha` is read only by FDL_LEAKY_RELU.  Formulas are the
+ * reference's: relu fmaxf(0,x); leaky x>0?x:alpha*x; gelu tanh approximation with
+ * 0.79788456 and 0.044715; sigmoid 1/(1+expf(-x)); tanh tanhf(x).  Replaces
+ * dl::kernels::activation (include/dl/kernels/activation.hpp:17,
+ * src/kernels/cuda/activation.cu:6-94). */
+int fdl_unary_f32(const float* x, float* out, int64_t n, int op, float alpha,
+                  void* stream);
+
+/* out[i] = max(0, fl(fl(a[i]*b[i]) + c[i])): the chain relu(a*b + c) in one pass with
+ * the two roundings the reference's three separate kernels produce (no FMA).
+ * Fuses ops::mul -> ops::add -> ops::relu (src/ops/Elementwise.cpp:36-50,
+ * src/ops/Activation.cpp:13-28). */
+int fdl_mul_add_relu_f32(const float* a, const float* b, const float* c, float* out,
+                         int64_t n, void* stream);
+
+/* In place: out[r*cols + c] += bias[c].  Replaces dl::kernels::add_row_bias
+ * (include/dl/kernels/bias.hpp:5, src/kernels/cuda/bias.cu:5-28). */
+int fdl_add_row_bias_f32(float* out, const float* bias, int64_t rows, int64_t cols,
+                         void* stream);
+
+/* In place: out[r*cols + c] = max(0, out[r*cols + c] + bias[c]): the bias epilogue of
+ * ops::linear followed by nn::ReLU in one pass (src/ops/Linear.cpp:38-45,
+ * src/nn/ReLU.cpp:7-9). */
+int fdl_add_row_bias_relu_f32(float* out, const float* bias, int64_t rows, int64_t cols,
+                              void* stream);
+
+/* Broadcasting binary op.  `ndim` (1..8) dimensions, `shape` is the OUTPUT shape,
+ * `a_strides`/`b_strides` are element strides of each operand per output dimension
+ * with 0 in broadcast dimensions (NumPy rules; the host precomputes them).  The
+ * output is contiguous row-major.  The library collapses dimensions and derives
+ * division-free index arithmetic on the host before launching.
+ * The reference has no general broadcast (its binary ops demand equal shapes,
+ * src/ops/OpUtils.cpp:74-101); its one broadcast is the row-bias kernel
+ * (src/kernels/cuda/bias.cu:5-12), of which this is the out-of-place generalisation. */
+int fdl_broadcast_binary_f32(const float* a, const float* b, float* out, int ndim,
+                             const int64_t* shape, const int64_t* a_strides,
+                             const int64_t* b_strides, int op, void* stream);
+
+/* ---- reductions ------------------------------------------------------------------- */
+
+/* out[k] = sum of x[1024k .. 1024k+1023] for k in [0, n/1024) with the exact pairing
+ * order of the reference's shared-memory trees, so results are bit-identical to them:
+ * FDL_TREE_ADDRESS pairs (i, i+s) for s = 512..1, FDL_TREE_INTERLEAVE for s = 1..512.
+ * A tail of n % 1024 elements is ignored, as in the reference.  Replaces
+ * dl::kernels::reduction (include/dl/kernels/reduction.hpp:14-15,
+ * src/kernels/cuda/reduction.cu:8-57,75-85). */
+int fdl_block_reduce_1024_f32(const float* x, float* out, int64_t n, int tree,
+                              void* stream);
+
+/* Scratch bytes fdl_sum_f32 / fdl_reduce_cols_f32 need for the given problem.
+ * Always a multiple of 256; the scratch pointer must be 256-byte aligned. */
+size_t fdl_sum_scratch_bytes(int64_t n);
+size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols);
+
+/* out_f32[0] = sum of x[0..n).  If out_f64 is not NULL it also receives the sum
+ * before the final rounding to float (what a multi-GPU caller all-reduces).
+ * Deterministic: same input, same launch -> same bits.  `scratch` may be NULL, in
+ * which case the library uses a per-device workspace it allocates on first use and
+ * keeps; otherwise it must hold fdl_sum_scratch_bytes(n).  No counterpart in the
+ * reference, whose reduction stops at one partial per 1024 elements
+ * (src/kernels/cuda/reduction.cu:34-57). */
+int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64,
+                void* scratch, size_t scratch_bytes, void* stream);
+
+/* Row-wise reduction of a row-major [rows, cols] matrix along axis 1:
+ * out[r] = op over c of x[r, c]; FDL_REDUCE_MAX ignores NaNs like fmaxf.  No counterpart
+ * in the reference (row max / row sum exist only inside its softmax,
+ * src/kernels/cuda/softmax.cu:157-221). */
+int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,
+                        void* stream);
+
+/* out[r] = lowest column index of the row maximum (NaN compares as -inf).  int64
+ * output.  No counterpart in the reference. */
+int fdl_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, int64_t* out,
+                        void* stream);
+
+/* Column-wise reduction along axis 0 of `batch` stacked row-major [rows, cols]
+ * matrices: out[b, c] = scale-free op over r of x[b, r, c].  FDL_REDUCE_MEAN divides
+ * by `mean_divisor` (pass rows, or the global row count when rows are one shard of a
+ * larger tensor and the caller all-reduces sums itself).  Scratch as in fdl_sum_f32.
+ * No counterpart in the reference. */
+int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t cols,
+                        float* out, int op, double mean_divisor, void* scratch,
+                        size_t scratch_bytes, void* stream);
+
+/* ---- row-wise normalisations ---------------------------------------------------------- */
+
+/* y[r, c] = exp(x[r, c] - max_r) * (1 / sum_c exp(x[r, c] - max_r)).  Replaces
+ * dl::kernels::softmax for every SoftmaxAlgo value (include/dl/kernels/softmax.hpp:15-16,
+ * src/kernels/cuda/softmax.cu:28-254,272-285). */
+int fdl_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols,
+                         void* stream);
+
+/* y[r, c] = (x[r, c] - mean_r) * rstd_r * gamma[c] + beta[c] with
+ * rstd_r = 1/sqrt(var_r + eps), biased variance.  gamma and beta may each be NULL
+ * (treated as 1 and 0), which gives the reference's affine-free form.  If `mean_out` /
+ * `rstd_out` are not NULL they receive the per-row statistics.  Replaces
+ * dl::kernels::layernorm (include/dl/kernels/layernorm.hpp:5-6,
+ * src/kernels/cuda/layernorm.cu:9-78). */
+int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta,
+                           float* y, float* mean_out, float* rstd_out, int64_t rows,
+                           int64_t cols, float eps, void* stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* FDL_KERNELS_H_ */
