@@ -44,6 +44,11 @@ PROTOTYPES = {
     "fdl_reduce_cols_f32": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f64, _vp, _sz, _vp]),
     "fdl_softmax_rows_f32": (_int, [_vp, _vp, _i64, _i64, _vp]),
     "fdl_layernorm_rows_f32": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp]),
+    "fdl_host_binary_f32": (_int, [_vp, _vp, _vp, _i64, _int]),
+    "fdl_host_unary_f32": (_int, [_vp, _vp, _i64, _int, _f32]),
+    "fdl_host_mul_add_relu_f32": (_int, [_vp, _vp, _vp, _vp, _i64]),
+    "fdl_host_row_broadcast_f32": (_int, [_vp, _vp, _vp, _i64, _i64, _int]),
+    "fdl_host_sum_f32": (_int, [_vp, _i64, C.POINTER(C.c_double)]),
 }
 
 
@@ -262,3 +267,35 @@ def layernorm_rows(x, gamma=None, beta=None, eps=1e-5, out=None, want_stats=Fals
 
 def take_device_error() -> None:
     check(lib().fdl_take_device_error(), "device-side wait")
+
+
+# ---- host-buffer entry points (torch CPU tensors, ideally pinned) ------------------------------
+
+
+def host_binary(a, b, out, op):
+    check(lib().fdl_host_binary_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), op), "fdl_host_binary_f32")
+    return out
+
+
+def host_unary(x, out, op, alpha=0.01):
+    check(lib().fdl_host_unary_f32(_ptr(x), _ptr(out), x.numel(), op, alpha), "fdl_host_unary_f32")
+    return out
+
+
+def host_mul_add_relu(a, b, c, out):
+    check(lib().fdl_host_mul_add_relu_f32(_ptr(a), _ptr(b), _ptr(c), _ptr(out), a.numel()),
+          "fdl_host_mul_add_relu_f32")
+    return out
+
+
+def host_row_broadcast(a, row, out, op):
+    rows, cols = a.shape
+    check(lib().fdl_host_row_broadcast_f32(_ptr(a), _ptr(row), _ptr(out), rows, cols, op),
+          "fdl_host_row_broadcast_f32")
+    return out
+
+
+def host_sum(x) -> float:
+    res = C.c_double(0.0)
+    check(lib().fdl_host_sum_f32(_ptr(x), x.numel(), C.byref(res)), "fdl_host_sum_f32")
+    return res.value

@@ -201,6 +201,26 @@ int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta
                            float* y, float* mean_out, float* rstd_out, int64_t rows,
                            int64_t cols, float eps, void* stream);
 
+/* ---- host-buffer entry points ---------------------------------------------------------- */
+
+/* The same operations with HOST pointers (`h_*`): the library moves the data through a
+ * ring of device staging buffers on its own streams, overlapping upload, kernel and
+ * download, and returns when the result is in host memory.  They stand in for the
+ * reference's Tensor::from_host -> dl::ops::<op> -> Tensor::to_host round trip
+ * (include/dl/tensor/Tensor.hpp:97-121, src/tensor/TensorImpl.cpp:91-125) for callers
+ * whose tensors live on the host.  Buffers should be page-locked (pageable memory works
+ * but serialises the copies).  Staging memory (4 slots x 96 MiB per device) is allocated
+ * on first use and kept. */
+int fdl_host_binary_f32(const float* h_a, const float* h_b, float* h_out, int64_t n, int op);
+int fdl_host_unary_f32(const float* h_x, float* h_out, int64_t n, int op, float alpha);
+int fdl_host_mul_add_relu_f32(const float* h_a, const float* h_b, const float* h_c,
+                              float* h_out, int64_t n);
+/* h_out[r, c] = h_a[r, c] (op) h_row[c] */
+int fdl_host_row_broadcast_f32(const float* h_a, const float* h_row, float* h_out,
+                               int64_t rows, int64_t cols, int op);
+/* *h_out = sum of h_x[0..n) (double; chunk partials folded on the host in order). */
+int fdl_host_sum_f32(const float* h_x, int64_t n, double* h_out);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

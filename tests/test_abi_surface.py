@@ -1,0 +1,46 @@
+"""The C-ABI library loads on a machine without a GPU and exports what the header declares."""
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "fdl_kernels.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fdl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    assert "fdl_binary_f32" in names and "fdl_softmax_rows_f32" in names and len(names) >= 20
+
+
+def test_library_exports_every_declared_symbol(fdl):
+    handle = ctypes.CDLL(str(fdl.library_path()))
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"{name} is declared in include/fdl_kernels.h but not exported"
+
+
+def test_binding_covers_every_declared_symbol(fdl):
+    assert sorted(fdl.PROTOTYPES) == declared_symbols()
+
+
+def test_no_gpu_calls_needed_for_metadata(fdl):
+    lib = fdl.lib()
+    assert lib.fdl_version() >= 1000
+    assert lib.fdl_error_string(0) == b"success"
+    assert b"invalid" in lib.fdl_error_string(-1)
+    assert lib.fdl_sum_scratch_bytes(1 << 28) % 256 == 0
+    assert lib.fdl_reduce_cols_scratch_bytes(1, 8192, 8192) % 256 == 0
+
+
+def test_product_does_not_import_the_oracle():
+    """No file of the package may reach into oracle/ (no CPU fallback in the product)."""
+    for path in (ROOT / "fast_dl_b200").rglob("*"):
+        if path.suffix in {".py", ".cu", ".cuh", ".cpp", ".hpp", ".h"} and "build" not in path.parts[-3:-1]:
+            text = path.read_text()
+            if path.name == "build.py":
+                continue  # builds the checker, does not use it
+            assert "oracle" not in text, f"{path} mentions the oracle"

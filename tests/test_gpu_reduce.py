@@ -1,0 +1,141 @@
+"""GPU parity: reductions through the C ABI."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from oracle import ref
+from tests.helpers import assert_bit_exact, assert_sum_close, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(cuda, a):
+    return cuda.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("tree", [0, 1])
+@pytest.mark.parametrize("nblocks", [1, 7, 8, 9, 1000, 16384])
+def test_block_reduce_matches_reference_tree_bit_for_bit(fdl, cuda, tree, nblocks):
+    rng = np.random.default_rng(42)
+    x = rng.uniform(-1, 1, nblocks * 1024 + 17).astype(np.float32)  # the 17-element tail is ignored
+    got = to_np(fdl.block_reduce_1024(dev(cuda, x), tree))
+    assert_bit_exact(got, orc.block_reduce_1024(x, tree), f"tree {tree}")
+    # unaligned input takes the scalar-load path; same bits
+    xd = dev(cuda, np.concatenate([[0.0], x]).astype(np.float32))[1:]
+    assert_bit_exact(to_np(fdl.block_reduce_1024(xd, tree)), orc.block_reduce_1024(x, tree), "unaligned")
+
+
+def test_block_reduce_golden_and_reference_kernels(fdl, cuda, golden):
+    x = golden["seeded_reduce_input"]
+    assert_bit_exact(to_np(fdl.block_reduce_1024(dev(cuda, x), 0)), golden["seeded_reduce_interleave"], "golden i")
+    assert_bit_exact(to_np(fdl.block_reduce_1024(dev(cuda, x), 1)), golden["seeded_reduce_address"], "golden a")
+    if ref.available():
+        rng = np.random.default_rng(1)
+        big = dev(cuda, rng.uniform(-1, 1, 1 << 22).astype(np.float32))
+        for tree in (0, 1):
+            want = cuda.empty(big.numel() // 1024, dtype=cuda.float32, device="cuda")
+            cuda.cuda.synchronize()
+            ref.gpu_reduction(big.data_ptr(), want.data_ptr(), big.numel(), tree)
+            ref.gpu_sync()
+            assert_bit_exact(to_np(fdl.block_reduce_1024(big, tree)), to_np(want), f"reference kernel tree {tree}")
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 1023, 1025, 65536, 65537, (1 << 22) + 3, 1 << 26])
+def test_full_sum(fdl, cuda, n):
+    rng = np.random.default_rng(42)
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    out32, out64 = fdl.full_sum(dev(cuda, x), want_f64=True)
+    want = orc.full_sum(x)
+    norm = max(orc.norm2(x), 1e-30)
+    assert_sum_close(to_np(out32)[0], want, norm, f"sum n={n}")
+    assert_sum_close(to_np(out64)[0], want, norm, f"sum64 n={n}")
+    assert np.float32(to_np(out64)[0]) == to_np(out32)[0]
+
+
+def test_full_sum_is_deterministic_and_scratch_is_reusable(fdl, cuda):
+    rng = np.random.default_rng(2)
+    x = dev(cuda, rng.normal(size=(1 << 24) + 11).astype(np.float32))
+    first = to_np(fdl.full_sum(x))
+    for _ in range(5):
+        assert_bit_exact(to_np(fdl.full_sum(x)), first, "repeat")
+    nbytes = fdl.lib().fdl_sum_scratch_bytes(x.numel())
+    scratch = cuda.zeros(nbytes, dtype=cuda.uint8, device="cuda")
+    for _ in range(3):
+        assert_bit_exact(to_np(fdl.full_sum(x, scratch=scratch)), first, "caller scratch")
+    with pytest.raises(fdl.FdlError):
+        fdl.full_sum(x, scratch=scratch[:64])
+    unaligned = dev(cuda, np.concatenate([[0.0], to_np(x)]).astype(np.float32))[1:]
+    assert_sum_close(to_np(fdl.full_sum(unaligned))[0], orc.full_sum(to_np(x)), orc.norm2(to_np(x)), "unaligned")
+
+
+SHAPES = [(1, 1), (1, 7), (5, 3), (17, 128), (33, 1000), (64, 2048), (9, 2052), (300, 4096), (3, 100003),
+          (2048, 33), (1024, 1024)]
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_row_reductions(fdl, cuda, rows, cols):
+    rng = np.random.default_rng(42)
+    x = rng.normal(size=(rows, cols)).astype(np.float32)
+    xd = dev(cuda, x)
+    norm = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
+    assert_sum_close(to_np(fdl.reduce_rows(xd, fdl.REDUCE_SUM)), orc.reduce_rows(x, 0), norm, "row sum")
+    assert_sum_close(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MEAN)), orc.reduce_rows(x, 1), norm / cols, "row mean")
+    assert_bit_exact(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "row max")
+    np.testing.assert_array_equal(to_np(fdl.argmax_rows(xd)), orc.argmax_rows(x))
+
+
+def test_argmax_ties_nan_inf(fdl, cuda):
+    rng = np.random.default_rng(8)
+    x = rng.integers(0, 4, size=(512, 4096)).astype(np.float32)  # many ties
+    x[3, :] = -np.inf
+    x[4, :] = np.nan
+    x[5, 100] = np.inf
+    x[5, 50] = np.nan
+    x[6, ::2] = np.nan
+    got = to_np(fdl.argmax_rows(dev(cuda, x)))
+    np.testing.assert_array_equal(got, orc.argmax_rows(x))
+    assert got.dtype == np.int64 and got[3] == 0 and got[4] == 0 and got[5] == 100
+    small = rng.integers(0, 3, size=(1000, 37)).astype(np.float32)
+    np.testing.assert_array_equal(to_np(fdl.argmax_rows(dev(cuda, small))), orc.argmax_rows(small))
+    assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, x), fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "max with nan")
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES + [(8192, 256), (100000, 4)])
+def test_column_reductions(fdl, cuda, rows, cols):
+    rng = np.random.default_rng(42)
+    x = rng.normal(size=(rows, cols)).astype(np.float32)
+    xd = dev(cuda, x)
+    norm = np.sqrt((x.astype(np.float64) ** 2).sum(axis=0))
+    assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), orc.reduce_cols(x, 0), norm, "col sum")
+    assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN)), orc.reduce_cols(x, 1), norm / rows, "col mean")
+    assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX)), orc.reduce_cols(x, 2), "col max")
+    again = to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM))
+    assert_bit_exact(again, to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "deterministic")
+
+
+def test_column_reduction_batched_and_caller_scratch(fdl, cuda):
+    rng = np.random.default_rng(3)
+    x = rng.normal(size=(5, 700, 96)).astype(np.float32)
+    xd = dev(cuda, x)
+    got = to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN))
+    norm = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1)) / 700
+    assert_sum_close(got, orc.reduce_cols(x, 1), norm, "batched mean")
+    nbytes = fdl.lib().fdl_reduce_cols_scratch_bytes(5, 700, 96)
+    scratch = cuda.zeros(max(nbytes, 256), dtype=cuda.uint8, device="cuda")
+    for _ in range(2):
+        assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN, scratch=scratch)), got, "caller scratch")
+
+
+def test_config3_shapes(fdl, cuda):
+    """X[8192,8192] ~ N(0,1): sum/max axis 1, mean axis 0, argmax axis 1, full sum."""
+    rng = np.random.default_rng(42)
+    x = rng.standard_normal((8192, 8192), dtype=np.float32)
+    xd = dev(cuda, x)
+    x64 = x.astype(np.float64)
+    n1 = np.sqrt((x64 ** 2).sum(axis=1))
+    n0 = np.sqrt((x64 ** 2).sum(axis=0))
+    assert_sum_close(to_np(fdl.reduce_rows(xd, fdl.REDUCE_SUM)), x64.sum(axis=1), n1, "sum axis 1")
+    assert_bit_exact(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MAX)), x.max(axis=1), "max axis 1")
+    assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN)), x64.mean(axis=0), n0 / 8192, "mean axis 0")
+    np.testing.assert_array_equal(to_np(fdl.argmax_rows(xd)), x.argmax(axis=1))
+    assert_sum_close(to_np(fdl.full_sum(xd))[0], x64.sum(), np.sqrt((x64 ** 2).sum()), "full sum")

@@ -1,0 +1,120 @@
+"""GPU parity: row softmax and row layernorm through the C ABI."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from oracle import ref
+from tests.helpers import assert_close_scaled, to_np
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 1), (2, 4), (3, 5), (7, 128), (100, 132), (33, 1000), (64, 1024), (4096, 1024), (65, 2048),
+          (37, 2052), (19, 4096), (11, 8192), (5, 16384), (3, 16388), (2, 40000), (1001, 36), (50000, 8)]
+
+
+def dev(cuda, a):
+    return cuda.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_reference_literals(fdl, cuda, golden):
+    got = to_np(fdl.softmax_rows(dev(cuda, golden["softmax_input"])))
+    assert np.abs(got - golden["softmax_expected"]).max() <= 1e-4  # the reference test's tolerance
+    assert np.abs(got.sum(axis=1) - 1).max() <= 1e-4               # and its row-sum property
+    assert_close_scaled(got, golden["softmax_expected"], "softmax literal")
+    got = to_np(fdl.layernorm_rows(dev(cuda, golden["layernorm_input"]), eps=1e-5))
+    assert np.abs(got - golden["layernorm_expected"]).max() <= 1e-4
+    assert_close_scaled(got, golden["layernorm_expected"], "layernorm literal")
+    for key in ("softmax", "layernorm"):
+        x = golden[f"seeded_{key}_input"]
+        want = golden["seeded_softmax_bench"] if key == "softmax" else golden["seeded_layernorm_expected"]
+        fn = fdl.softmax_rows if key == "softmax" else fdl.layernorm_rows
+        assert_close_scaled(to_np(fn(dev(cuda, x))), want, f"seeded {key}")
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_softmax(fdl, cuda, rows, cols):
+    rng = np.random.default_rng(42)
+    x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+    got = to_np(fdl.softmax_rows(dev(cuda, x)))
+    assert_close_scaled(got, orc.softmax_rows(x), f"softmax {rows}x{cols}")
+    assert_close_scaled(got, orc.softmax_rows_f64(x), f"softmax vs f64 {rows}x{cols}")
+    assert np.abs(got.astype(np.float64).sum(axis=1) - 1).max() <= 1e-5
+    fdl.take_device_error()
+
+
+def test_softmax_reference_benchmark_case(fdl, cuda):
+    """4096 x 1024 uniform[-10, 10], the reference benchmark's case and tolerance."""
+    rng = np.random.default_rng(42)
+    x = rng.uniform(-10, 10, (4096, 1024)).astype(np.float32)
+    xd = dev(cuda, x)
+    got = to_np(fdl.softmax_rows(xd))
+    assert_close_scaled(got, orc.softmax_rows(x), "bench case")
+    if ref.available():
+        for algo in (0, 1, 2):
+            want = cuda.empty_like(xd)
+            cuda.cuda.synchronize()
+            ref.gpu_softmax(xd.data_ptr(), want.data_ptr(), 4096, 1024, algo)
+            ref.gpu_sync()
+            assert_close_scaled(got, to_np(want), f"reference kernel algo {algo}")
+
+
+def test_softmax_extremes(fdl, cuda):
+    x = np.zeros((4, 1024), dtype=np.float32)
+    x[0, :] = 1e30
+    x[1, 0] = 88.0
+    x[2, :] = -1e30
+    x[3, 5] = -np.inf
+    got = to_np(fdl.softmax_rows(dev(cuda, x)))
+    assert_close_scaled(got, orc.softmax_rows(x), "extremes")
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+@pytest.mark.parametrize("affine", [False, True])
+def test_layernorm(fdl, cuda, rows, cols, affine):
+    rng = np.random.default_rng(42)
+    x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+    g = rng.uniform(0.9, 1.1, cols).astype(np.float32) if affine else None
+    b = rng.uniform(-0.1, 0.1, cols).astype(np.float32) if affine else None
+    gd = dev(cuda, g) if affine else None
+    bd = dev(cuda, b) if affine else None
+    got, mean, rstd = fdl.layernorm_rows(dev(cuda, x), gd, bd, eps=1e-5, want_stats=True)
+    got = to_np(got)
+    if cols > 1:
+        assert_close_scaled(got, orc.layernorm_rows(x, g, b, 1e-5), f"layernorm {rows}x{cols}")
+    assert_close_scaled(got, orc.layernorm_rows_f64(x, g, b, 1e-5), f"layernorm vs f64 {rows}x{cols}")
+    x64 = x.astype(np.float64)
+    assert_close_scaled(to_np(mean), x64.mean(axis=1), "mean")
+    np.testing.assert_allclose(to_np(rstd), 1 / np.sqrt(x64.var(axis=1) + 1e-5), rtol=1e-5)
+    fdl.take_device_error()
+
+
+def test_layernorm_vs_reference_kernel(fdl, cuda):
+    if not ref.available():
+        pytest.skip("oracle/_ref/libref.so was not built")
+    rng = np.random.default_rng(42)
+    x = dev(cuda, rng.normal(0, 3, (4096, 1024)).astype(np.float32))
+    want = cuda.empty_like(x)
+    cuda.cuda.synchronize()
+    ref.gpu_layernorm(x.data_ptr(), want.data_ptr(), 4096, 1024, 1e-5)
+    ref.gpu_sync()
+    assert_close_scaled(to_np(fdl.layernorm_rows(x)), to_np(want), "reference kernel")
+
+
+def test_config4_shape(fdl, cuda):
+    """logits[65536,1024] ~ N(0,3); gamma ~ U[0.9,1.1], beta ~ U[-0.1,0.1], eps 1e-5.
+    Full size: checked through size-independent properties plus a sampled oracle comparison."""
+    rng = np.random.default_rng(42)
+    x = (rng.standard_normal((65536, 1024), dtype=np.float32) * np.float32(3))
+    g = rng.uniform(0.9, 1.1, 1024).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, 1024).astype(np.float32)
+    xd = dev(cuda, x)
+    sm = to_np(fdl.softmax_rows(xd))
+    assert np.abs(sm.astype(np.float64).sum(axis=1) - 1).max() <= 1e-5
+    assert (sm >= 0).all() and np.array_equal(sm.argmax(axis=1), x.argmax(axis=1))
+    pick = rng.choice(65536, 512, replace=False)
+    assert_close_scaled(sm[pick], orc.softmax_rows(x[pick]), "softmax sample")
+    ln = to_np(fdl.layernorm_rows(xd, dev(cuda, g), dev(cuda, b), eps=1e-5))
+    assert_close_scaled(ln[pick], orc.layernorm_rows(x[pick], g, b, 1e-5), "layernorm sample")
+    plain = to_np(fdl.layernorm_rows(xd)).astype(np.float64)
+    assert np.abs(plain.mean(axis=1)).max() <= 1e-5 and np.abs(plain.var(axis=1) - 1).max() <= 1e-4
+    fdl.take_device_error()
