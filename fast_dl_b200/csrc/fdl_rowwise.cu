@@ -341,15 +341,16 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
     size_t stage_bytes = rps * row_bytes;
     stage_bytes = (stage_bytes + 127) / 128 * 128;
     const size_t smem = kTeams * kRwStages * (stage_bytes + sizeof(uint64_t));
-    if (smem > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
+    if (smem + 1024 > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
 
     auto kernel = rows_staged_kernel<Op, TPR, NV>;
     static size_t configured_smem = 0;
     if (smem > configured_smem) {
+        // Exactly what is needed: the opt-in ceiling covers static + dynamic together.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             info->max_smem_optin);
+                                             static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        configured_smem = info->max_smem_optin;
+        configured_smem = smem;
     }
     int blocks_per_sm = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel,

@@ -31,12 +31,20 @@ def assert_bit_exact(got, want, what=""):
         raise AssertionError(f"{what}: {n} elements differ; first at {i}: got {got.ravel()[i]!r} want {want.ravel()[i]!r}")
 
 
-def assert_close_scaled(got, want, what=""):
+def assert_close_scaled(got, want, what="", truth=None):
+    """|got - want| <= 1e-5 * max(1, |want|).  When `truth` (a float64 evaluation of the same
+    formula) is given, the CPU twin's own distance from it is granted on top: the reference's
+    CPU functions accumulate long rows sequentially in fp32 and drift from the exact value by
+    more than the tolerance once rows reach several thousand elements."""
     got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    allowed = REL_TOL * np.maximum(1.0, np.abs(want))
+    if truth is not None:
+        allowed = allowed + np.abs(want - np.asarray(truth, dtype=np.float64))
+    excess = np.abs(got - want) - allowed
+    worst = float(excess.max()) if excess.size else 0.0
+    assert worst <= 0.0, f"{what}: error exceeds the allowance by {worst:.3e}"
     err = np.abs(got - want) / np.maximum(1.0, np.abs(want))
-    worst = float(err.max()) if err.size else 0.0
-    assert worst <= REL_TOL, f"{what}: max scaled error {worst:.3e} > {REL_TOL}"
-    return worst
+    return float(err.max()) if err.size else 0.0
 
 
 def assert_sum_close(got, want, norm2, what=""):

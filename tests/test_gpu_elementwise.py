@@ -85,21 +85,29 @@ def test_exact_activations(fdl, cuda, n, op):
     assert_bit_exact(got, orc.unary(x, op, 0.01), ACT[op])
 
 
+# Distance allowed against the CPU twins.  The kernels call the same CUDA math functions as
+# the reference's kernels (and match those bit for bit, next test); CUDA documents expf and
+# tanhf to 2 ulp of the true value and glibc's are good to 1 ulp, so two correct results can
+# sit 3 ulp apart.  gelu and sigmoid stay within 2 ulp of the CPU twin on these inputs.
+CPU_TWIN_ULP = {2: 2, 3: 2, 4: 3}
+
+
 @pytest.mark.parametrize("op", [2, 3, 4])
 def test_transcendental_activations_vs_cpu(fdl, cuda, golden, op):
-    """<= 2 ulp against the CPU functions of the reference's activation test."""
+    """Against the CPU functions of the reference's activation test (golden vectors)."""
     for key in ("activation_input", "seeded_activation_input"):
         x = golden[key]
         want = golden[("activation_expected_" if key == "activation_input" else "seeded_activation_") + ACT[op]]
         got = to_np(fdl.unary(dev(cuda, x), op, 0.01))
+        assert np.abs(got[np.isfinite(want)] - want[np.isfinite(want)]).max() < 1e-5  # the reference test's check
         ulp = orc.ulp_distance(got, want)
+        ok = ulp <= CPU_TWIN_ULP[op]
         if op == 2:
             # 1 + tanh(u) cancels for u << 0; there the reference formula itself only promises
             # absolute accuracy of a few ulp of 0.5*|x|, so the ulp test is applied to that scale.
-            slack = 2 * np.spacing(np.abs(0.5 * x).astype(np.float32)).astype(np.float64)
-            ok = (ulp <= 2) | (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= slack)
-        else:
-            ok = ulp <= 2
+            with np.errstate(invalid="ignore"):
+                slack = 2 * np.spacing(np.abs(0.5 * x).astype(np.float32)).astype(np.float64)
+                ok |= np.abs(got.astype(np.float64) - want.astype(np.float64)) <= slack
         ok |= np.isnan(got) & np.isnan(want)
         assert ok.all(), f"{ACT[op]}: max ulp {ulp[~ok].max()} at x={x[~ok][:4]}"
 
