@@ -247,7 +247,8 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    rows = ROWS // world + (1 if rank < ROWS % world else 0)
+    total_rows = args.rows
+    rows = total_rows // world + (1 if rank < total_rows % world else 0)
     n = rows * COLS
     dev = torch.device("cuda", local)
     gen = torch.Generator(device=dev).manual_seed(42 + rank)
@@ -307,8 +308,11 @@ def run_ours(args) -> None:
     per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)) / K for i in range(3)]
 
     # ---- end to end through the host-buffer entry points ------------------------------------------
-    ha, hb, hc, hrow = host_inputs(rows, 1000 + rank, pinned=True)
-    ha2, hc2 = ha.view(rows, COLS), hc.view(rows, COLS)
+    need_host = not args.no_e2e or (rank == 0 and world == 1 and not args.no_cpu)
+    ha = hb = hc = hrow = ha2 = hc2 = None
+    if need_host:
+        ha, hb, hc, hrow = host_inputs(rows, 1000 + rank, pinned=True)
+        ha2, hc2 = ha.view(rows, COLS), hc.view(rows, COLS)
 
     def e2e_step():
         capi.host_binary(ha, hb, hc, capi.ADD)
@@ -320,14 +324,16 @@ def run_ours(args) -> None:
             s = float(t.item())
         return s
 
-    e2e_steps = max(2, min(5, K))
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    e2e_steps = 0 if args.no_e2e else max(2, min(5, K))
+    e2e_sec = float("nan")
+    if e2e_steps:
         e2e_step()
-    barrier()
-    e2e_sec = (time.perf_counter() - t0) / e2e_steps
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_sec = (time.perf_counter() - t0) / e2e_steps
 
     # ---- reduce over ranks ------------------------------------------------------------------------------
     stats = torch.tensor([ms_total, e2e_sec, *per_op], dtype=torch.float64, device=dev)
@@ -335,7 +341,7 @@ def run_ours(args) -> None:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     ms_total, e2e_sec, t_add, t_bc, t_sum = stats.tolist()
 
-    total_bytes = sum(algorithmic_bytes(ROWS, COLS).values()) + (world - 1) * (4 * COLS + 4)
+    total_bytes = sum(algorithmic_bytes(total_rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
     value = total_bytes * K / (ms_total * 1e-3) / 1e9
     e2e_value = total_bytes / e2e_sec / 1e9
     peak, peak_kind = measured_peak_gbs()
@@ -347,7 +353,7 @@ def run_ours(args) -> None:
         "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "large_tensor_sweep_268435456_f32: add, row-broadcast add, full sum",
-                   "partition": f"leading dimension over {world} GPU(s), {rows} of {ROWS} rows on rank 0",
+                   "partition": f"leading dimension over {world} GPU(s), {rows} of {total_rows} rows on rank 0",
                    "l2": "inputs larger than L2 (six distinct tensors stream per step)"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "GB/s",
@@ -365,10 +371,12 @@ def run_ours(args) -> None:
         },
     }
 
+    if args.rows != ROWS:
+        line["config"]["workload"] += f" (REDUCED to {args.rows} rows for profiling; not a bench value)"
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
             cpu = CpuPath()
-            sample_rows = ROWS // 4
+            sample_rows = min(ROWS // 4, rows)
             np_host = (ha.numpy(), hb.numpy(), hc.numpy(), hrow.numpy())
             sec = time_cpu(cpu, np_host, sample_rows, steps=3, warmup=1)
             nb = sum(algorithmic_bytes(sample_rows, COLS).values())
@@ -404,6 +412,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="rows of the [rows, 16384] view; smaller than 16384 only for profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "fdl_set_device": (_int, [_int]),
     "fdl_stream_synchronize": (_int, [_vp]),
     "fdl_take_device_error": (_int, []),
+    "fdl_set_tuning": (_int, [C.c_char_p, _int]),
     "fdl_binary_f32": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
     "fdl_unary_f32": (_int, [_vp, _vp, _i64, _int, _f32, _vp]),
     "fdl_mul_add_relu_f32": (_int, [_vp, _vp, _vp, _vp, _i64, _vp]),
@@ -106,6 +107,10 @@ def _require(t, dtype=None):
     if dtype is not None and t.dtype != dtype:
         raise ValueError(f"expected dtype {dtype}, got {t.dtype}")
     return t
+
+
+def set_tuning(key: str, value: int) -> None:
+    check(lib().fdl_set_tuning(key.encode(), value), f"fdl_set_tuning({key})")
 
 
 def use_device(index: int) -> None:

@@ -38,6 +38,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Launch-shape knobs that the bench can vary to show why the defaults were chosen
+// (set through fdl_set_tuning).  Defaults are the measured best on B200.
+struct Tuning {
+    int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
+    int rows_staged = 1;   // row softmax/layernorm: 1 = bulk-async ring, 2 = one bulk copy per CTA, 0 = direct loads
+};
+Tuning& tuning();
+
 // Per-device workspace the library owns (allocated on first use, grown on demand,
 // never freed before process exit).  Used when a caller passes scratch == NULL.
 int get_workspace(size_t bytes, void** out);

@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(kBlkThreads)
 block_reduce_1024_kernel(const float* x, float* out, int64_t nblocks) {
     const int lane = threadIdx.x & (kWarp - 1);
     const int warp = threadIdx.x / kWarp;
+    // One 1024-block per warp, eight per CTA; the grid covers every block once (the loop
+    // only matters beyond 2^31 CTAs).
     for (int64_t blk = static_cast<int64_t>(blockIdx.x) * kBlkWarps + warp; blk < nblocks;
          blk += static_cast<int64_t>(gridDim.x) * kBlkWarps) {
         const float* src = x + blk * kBlk;
@@ -139,9 +141,11 @@ block_reduce_1024_kernel(const float* x, float* out, int64_t nblocks) {
 // Shared pieces of the grid-wide reductions
 // ======================================================================================
 
-constexpr int kSumThreads = 512;
-constexpr int kSumUnroll = 4;
-constexpr int kSumCluster = 4;  // CTAs per cluster; partials are folded through DSMEM
+constexpr int kSumThreads = 256;
+constexpr int kSumUnroll = 8;                                  // 128-bit loads per thread per tile
+constexpr int kSumTile = kSumThreads * kSumUnroll;             // float4 per tile (32 KiB)
+constexpr int kSumMaxCluster = 8;
+constexpr int kSumMaxPartials = 8192;                          // doubles in scratch
 constexpr int kCounterBytes = 256;
 
 // Block-wide sum in double; result valid in thread 0.  `red` holds one slot per warp.
@@ -165,78 +169,93 @@ __device__ __forceinline__ double block_sum_double(double v, double* red) {
 // Full sum
 // ======================================================================================
 //
+// Every CTA sums one 32 KiB tile (more only when the input exceeds 2 TiB) and the block
+// scheduler balances tiles over the SMs.  CL CTAs form a cluster: each drops its partial
+// into the leader's shared memory (DSMEM), the leader adds them in rank order and writes
+// one double per cluster to scratch.  The last cluster to arrive (ticket counter) folds
+// the per-cluster partials in index order, so the result does not depend on scheduling.
+//
 // Scratch layout: [0,256): uint32 arrival counter (zero between launches);
 // [256, ...): one double per cluster.
 
+template <int CL, bool VEC>
 __global__ void __launch_bounds__(kSumThreads)
-sum_kernel(const float* x, int64_t n, int64_t nvec, bool vec, float* out_f32, double* out_f64,
+sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_f64,
            unsigned int* counter, double* partials) {
     __shared__ double red[kSumThreads / kWarp];
-    __shared__ double cluster_slots[kSumCluster];
+    __shared__ double cluster_slots[kSumMaxCluster];
     __shared__ bool is_last;
 
     cg::cluster_group cluster = cg::this_cluster();
     // Arrive now, wait just before the first remote shared-memory access: by then every
     // CTA of the cluster is known to be running, which DSMEM stores require.
-    cluster.barrier_arrive();
-    const int64_t tid = static_cast<int64_t>(blockIdx.x) * kSumThreads + threadIdx.x;
-    const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kSumThreads;
+    if (CL > 1) cluster.barrier_arrive();
 
     float acc = 0.0f;
-    if (vec) {
+    if (VEC) {
         const float4* xv = reinterpret_cast<const float4*>(x);
-        float4 a[kSumUnroll];
-#pragma unroll
-        for (int u = 0; u < kSumUnroll; ++u) a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        int64_t i = tid;
-        for (; i + (kSumUnroll - 1) * nthreads < nvec; i += kSumUnroll * nthreads) {
+        for (int64_t tile = blockIdx.x; tile * kSumTile < nvec; tile += gridDim.x) {
+            const int64_t base = tile * kSumTile + threadIdx.x;
             float4 v[kSumUnroll];
+            if (base + (kSumUnroll - 1) * kSumThreads < nvec) {
 #pragma unroll
-            for (int u = 0; u < kSumUnroll; ++u) v[u] = ld_stream(xv + i + u * nthreads);
+                for (int u = 0; u < kSumUnroll; ++u) v[u] = ld_stream(xv + base + u * kSumThreads);
+            } else {
 #pragma unroll
-            for (int u = 0; u < kSumUnroll; ++u) {
-                a[u].x += v[u].x; a[u].y += v[u].y; a[u].z += v[u].z; a[u].w += v[u].w;
+                for (int u = 0; u < kSumUnroll; ++u) {
+                    v[u] = base + u * kSumThreads < nvec ? ld_stream(xv + base + u * kSumThreads)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
-        }
-        for (; i < nvec; i += nthreads) {
-            const float4 v = ld_stream(xv + i);
-            a[0].x += v.x; a[0].y += v.y; a[0].z += v.z; a[0].w += v.w;
-        }
-        float s[kSumUnroll];
+            float s[kSumUnroll];
 #pragma unroll
-        for (int u = 0; u < kSumUnroll; ++u) s[u] = (a[u].x + a[u].y) + (a[u].z + a[u].w);
-        acc = (s[0] + s[1]) + (s[2] + s[3]);
-        for (int64_t j = nvec * 4 + tid; j < n; j += nthreads) acc += x[j];
-    } else {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int64_t i = tid;
-        for (; i + 3 * nthreads < n; i += 4 * nthreads) {
-            const float v0 = ld_stream(x + i), v1 = ld_stream(x + i + nthreads);
-            const float v2 = ld_stream(x + i + 2 * nthreads), v3 = ld_stream(x + i + 3 * nthreads);
-            a0 += v0; a1 += v1; a2 += v2; a3 += v3;
+            for (int u = 0; u < kSumUnroll; ++u) s[u] = (v[u].x + v[u].y) + (v[u].z + v[u].w);
+            acc += ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
         }
-        for (; i < n; i += nthreads) a0 += ld_stream(x + i);
-        acc = (a0 + a1) + (a2 + a3);
+        // The n % 4 trailing floats.
+        if (blockIdx.x == 0) {
+            for (int64_t j = nvec * 4 + threadIdx.x; j < n; j += kSumThreads) acc += x[j];
+        }
+    } else {
+        // Input not 16-byte aligned: same tiling with 32-bit loads.
+        constexpr int64_t kScalarTile = static_cast<int64_t>(kSumTile) * 4;
+        for (int64_t tile = blockIdx.x; tile * kScalarTile < n; tile += gridDim.x) {
+            const int64_t base = tile * kScalarTile + threadIdx.x;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+            for (int u = 0; u < kSumUnroll * 4; ++u) {
+                const int64_t j = base + static_cast<int64_t>(u) * kSumThreads;
+                if (j < n) s4[u & 3] += ld_stream(x + j);
+            }
+            acc += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+        }
     }
 
     const double block_total = block_sum_double<kSumThreads>(static_cast<double>(acc), red);
 
-    // Cluster stage: every CTA drops its partial into the leader's shared memory.
-    const unsigned int rank = cluster.block_rank();
-    cluster.barrier_wait();
-    if (threadIdx.x == 0) {
-        double* leader_slots = cluster.map_shared_rank(cluster_slots, 0);
-        leader_slots[rank] = block_total;
+    unsigned int nclusters = gridDim.x;
+    unsigned int cluster_id = blockIdx.x;
+    if (CL > 1) {
+        // Cluster stage: every CTA drops its partial into the leader's shared memory.
+        const unsigned int rank = cluster.block_rank();
+        cluster.barrier_wait();
+        if (threadIdx.x == 0) {
+            double* leader_slots = cluster.map_shared_rank(cluster_slots, 0);
+            leader_slots[rank] = block_total;
+        }
+        cluster.sync();
+        if (rank != 0) return;
+        nclusters = gridDim.x / CL;
+        cluster_id = blockIdx.x / CL;
     }
-    cluster.sync();
-    if (rank != 0) return;
 
-    const unsigned int nclusters = gridDim.x / kSumCluster;
-    const unsigned int cluster_id = blockIdx.x / kSumCluster;
     if (threadIdx.x == 0) {
-        double t = 0.0;
+        double t = block_total;
+        if (CL > 1) {
+            t = 0.0;
 #pragma unroll
-        for (int k = 0; k < kSumCluster; ++k) t += cluster_slots[k];
+            for (int k = 0; k < CL; ++k) t += cluster_slots[k];
+        }
         partials[cluster_id] = t;
         __threadfence();
         const unsigned int ticket = atomicAdd(counter, 1u);
@@ -257,27 +276,35 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, bool vec, float* out_f32, do
     }
 }
 
-int sum_grid(const DeviceInfo* info, int* grid_out) {
-    static int clusters = 0;
-    if (clusters == 0) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(kSumCluster * 64);
-        cfg.blockDim = dim3(kSumThreads);
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = kSumCluster;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, sum_kernel, &cfg);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        clusters = n > 0 ? n : 1;
+template <int CL, bool VEC>
+int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsigned int* counter,
+               double* partials, cudaStream_t stream) {
+    const int64_t nvec = VEC ? n / 4 : 0;
+    int64_t tiles = VEC ? ceil_div(nvec, kSumTile) : ceil_div(n, static_cast<int64_t>(kSumTile) * 4);
+    if (tiles < 1) tiles = 1;
+    int64_t grid = ceil_div(tiles, CL) * CL;
+    const int64_t cap = static_cast<int64_t>(kSumMaxPartials) * CL;
+    if (grid > cap) grid = cap;
+    if (CL == 1) {
+        sum_kernel<1, VEC><<<static_cast<unsigned int>(grid), kSumThreads, 0, stream>>>(
+            x, n, nvec, out_f32, out_f64, counter, partials);
+        return launch_status();
     }
-    (void)info;
-    *grid_out = clusters * kSumCluster;
-    return FDL_OK;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned int>(grid));
+    cfg.blockDim = dim3(kSumThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CL;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sum_kernel<CL, VEC>, x, n, nvec, out_f32, out_f64,
+                                       counter, partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_status();
 }
 
 // ======================================================================================
@@ -410,12 +437,11 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
 template <class R, int TPR, int W>
 int launch_rows_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
                     cudaStream_t stream) {
-    int status = FDL_OK;
-    const DeviceInfo* info = current_device_info(&status);
-    if (info == nullptr) return status;
     constexpr int kRowsPerCta = kRowThreads / TPR;
-    const int grid = persistent_grid(info, 8, ceil_div(rows, kRowsPerCta));
-    reduce_rows_kernel<R, TPR, W><<<grid, kRowThreads, 0, stream>>>(
+    // One CTA per group of rows; the block scheduler balances them over the SMs.
+    int64_t grid = ceil_div(rows, kRowsPerCta);
+    if (grid > 2147483647) grid = 2147483647;
+    reduce_rows_kernel<R, TPR, W><<<static_cast<unsigned int>(grid), kRowThreads, 0, stream>>>(
         x, rows, static_cast<int>(cols), out, static_cast<float>(cols));
     return launch_status();
 }
@@ -476,43 +502,55 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     const int64_t b = blockIdx.z;
     const float* xb = x + b * rows * cols;
 
-    float acc[2][W];
+    constexpr int kInFlight = 4;  // rows in flight per thread
+    float acc[kInFlight][W];
 #pragma unroll
-    for (int k = 0; k < W; ++k) acc[0][k] = acc[1][k] = R::identity();
+    for (int u = 0; u < kInFlight; ++u) {
+#pragma unroll
+        for (int k = 0; k < W; ++k) acc[u][k] = R::identity();
+    }
 
     const int64_t r_begin = static_cast<int64_t>(chunk) * rows_per_chunk;
     int64_t r_end = r_begin + rows_per_chunk;
     if (r_end > rows) r_end = rows;
     if (col < cols) {
+        const float* xc = xb + col;
         int64_t r = r_begin + ry;
-        // Two rows in flight per thread.
-        for (; r + ty_count < r_end; r += 2 * ty_count) {
-            if (W == 4) {
-                const float4 v0 = ld_stream(reinterpret_cast<const float4*>(xb + r * cols + col));
-                const float4 v1 =
-                    ld_stream(reinterpret_cast<const float4*>(xb + (r + ty_count) * cols + col));
-                acc[0][0] = R::combine(acc[0][0], v0.x); acc[0][1 % W] = R::combine(acc[0][1 % W], v0.y);
-                acc[0][2 % W] = R::combine(acc[0][2 % W], v0.z); acc[0][3 % W] = R::combine(acc[0][3 % W], v0.w);
-                acc[1][0] = R::combine(acc[1][0], v1.x); acc[1][1 % W] = R::combine(acc[1][1 % W], v1.y);
-                acc[1][2 % W] = R::combine(acc[1][2 % W], v1.z); acc[1][3 % W] = R::combine(acc[1][3 % W], v1.w);
-            } else {
-                acc[0][0] = R::combine(acc[0][0], ld_stream(xb + r * cols + col));
-                acc[1][0] = R::combine(acc[1][0], ld_stream(xb + (r + ty_count) * cols + col));
+        for (; r + (kInFlight - 1) * ty_count < r_end; r += kInFlight * ty_count) {
+            float v[kInFlight][W];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const float* src = xc + (r + u * ty_count) * cols;
+                if (W == 4) {
+                    const float4 t = ld_stream(reinterpret_cast<const float4*>(src));
+                    v[u][0] = t.x; v[u][1 % W] = t.y; v[u][2 % W] = t.z; v[u][3 % W] = t.w;
+                } else {
+                    v[u][0] = ld_stream(src);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+#pragma unroll
+                for (int k = 0; k < W; ++k) acc[u][k] = R::combine(acc[u][k], v[u][k]);
             }
         }
         for (; r < r_end; r += ty_count) {
+            const float* src = xc + r * cols;
             if (W == 4) {
-                const float4 v0 = ld_stream(reinterpret_cast<const float4*>(xb + r * cols + col));
-                acc[0][0] = R::combine(acc[0][0], v0.x); acc[0][1 % W] = R::combine(acc[0][1 % W], v0.y);
-                acc[0][2 % W] = R::combine(acc[0][2 % W], v0.z); acc[0][3 % W] = R::combine(acc[0][3 % W], v0.w);
+                const float4 t = ld_stream(reinterpret_cast<const float4*>(src));
+                acc[0][0] = R::combine(acc[0][0], t.x); acc[0][1 % W] = R::combine(acc[0][1 % W], t.y);
+                acc[0][2 % W] = R::combine(acc[0][2 % W], t.z); acc[0][3 % W] = R::combine(acc[0][3 % W], t.w);
             } else {
-                acc[0][0] = R::combine(acc[0][0], ld_stream(xb + r * cols + col));
+                acc[0][0] = R::combine(acc[0][0], ld_stream(src));
             }
         }
     }
     const int tile_w = tx * W;
 #pragma unroll
-    for (int k = 0; k < W; ++k) tile[ry * tile_w + cx * W + k] = R::combine(acc[0][k], acc[1][k]);
+    for (int k = 0; k < W; ++k) {
+        tile[ry * tile_w + cx * W + k] =
+            R::combine(R::combine(acc[0][k], acc[1][k]), R::combine(acc[2][k], acc[3][k]));
+    }
     __syncthreads();
 
     // Fold the TY rows of the tile (fixed order) -- threads 0..tile_w-1 own one column each.
@@ -566,10 +604,11 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     g->tx = tx;
     g->col_blocks = static_cast<int>(ceil_div(packs, tx));
     const int ty = kColThreads / tx;
-    // Aim for ~8 CTAs per SM, but keep at least 4 rows per thread in a chunk.
-    const int64_t target = static_cast<int64_t>(sm_count) * 8;
+    // Many more CTAs than SMs (the block scheduler balances them), but at least 16 rows
+    // per thread in a chunk so that partials stay a small fraction of the traffic.
+    const int64_t target = static_cast<int64_t>(sm_count) * 32;
     int64_t chunks = ceil_div(target, static_cast<int64_t>(g->col_blocks) * batch);
-    const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 4);
+    const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 16);
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks < 1) chunks = 1;
     if (chunks > 65535) chunks = 65535;
@@ -614,7 +653,9 @@ int fdl_block_reduce_1024_f32(const float* x, float* out, int64_t n, int tree, v
     int status = FDL_OK;
     const DeviceInfo* info = current_device_info(&status);
     if (info == nullptr) return status;
-    const int grid = persistent_grid(info, 8, ceil_div(nblocks, kBlkWarps));
+    (void)info;
+    int64_t want_grid = ceil_div(nblocks, kBlkWarps);
+    const int grid = want_grid > 2147483647 ? 2147483647 : static_cast<int>(want_grid);
     cudaStream_t s = as_stream(stream);
     const bool vec = aligned16(x);
     if (tree == FDL_TREE_ADDRESS) {
@@ -629,8 +670,7 @@ int fdl_block_reduce_1024_f32(const float* x, float* out, int64_t n, int tree, v
 
 size_t fdl_sum_scratch_bytes(int64_t n) {
     (void)n;
-    // One double per cluster; the cluster count is bounded by SMs * resident CTAs.
-    return kCounterBytes + 4096 * sizeof(double);
+    return kCounterBytes + kSumMaxPartials * sizeof(double);
 }
 
 int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* scratch,
@@ -638,8 +678,6 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void
     if (n < 0 || (out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
     if (n > 0 && x == nullptr) return FDL_ERR_INVALID_ARGUMENT;
     int status = FDL_OK;
-    const DeviceInfo* info = current_device_info(&status);
-    if (info == nullptr) return status;
     const size_t need = fdl_sum_scratch_bytes(n);
     if (scratch == nullptr) {
         status = get_workspace(need, &scratch);
@@ -647,34 +685,20 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void
     } else if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) {
         return FDL_ERR_WORKSPACE;
     }
-    int grid = 0;
-    status = sum_grid(info, &grid);
-    if (status != FDL_OK) return status;
-    // Small inputs do not need the whole machine: one cluster per 64 KiB, at least one.
-    const int64_t want = ceil_div(n, int64_t{16384} * kSumCluster) * kSumCluster;
-    if (want < grid) grid = want < kSumCluster ? kSumCluster : static_cast<int>(want);
-    if (grid / kSumCluster > 4096) grid = 4096 * kSumCluster;
-
-    const bool vec = aligned16(x);
-    const int64_t nvec = vec ? n / 4 : 0;
     unsigned int* counter = static_cast<unsigned int*>(scratch);
     double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
-
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kSumThreads);
-    cfg.stream = as_stream(stream);
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = kSumCluster;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, sum_kernel, x, n, nvec, vec, out_f32, out_f64,
-                                       counter, partials);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    return launch_status();
+    cudaStream_t s = as_stream(stream);
+    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s);
+    switch (tuning().sum_cluster) {
+        case 1:
+            return launch_sum<1, true>(x, n, out_f32, out_f64, counter, partials, s);
+        case 2:
+            return launch_sum<2, true>(x, n, out_f32, out_f64, counter, partials, s);
+        case 4:
+            return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s);
+        default:
+            return launch_sum<8, true>(x, n, out_f32, out_f64, counter, partials, s);
+    }
 }
 
 int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,

@@ -82,6 +82,12 @@ __device__ __forceinline__ void team_sync() {
     else __syncthreads();
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---- per-row arithmetic on a register-resident row -----------------------------------------
 
 template <int TPR, int NV>
@@ -93,14 +99,18 @@ __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int 
         if (t + i * TPR < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     }
     m = team_max<TPR>(m, red);
+    // exp(x - m) as 2^((x - m) * log2(e)): the subtraction is the reference's own (exact
+    // for the terms that matter, by Sterbenz), then one multiply and one ex2.approx
+    // (relative error ~2^-22) instead of the ~9-instruction expf.
+    constexpr float kLog2e = 1.4426950408889634f;
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) {
-            v[i].x = expf(v[i].x - m);
-            v[i].y = expf(v[i].y - m);
-            v[i].z = expf(v[i].z - m);
-            v[i].w = expf(v[i].w - m);
+            v[i].x = fast_exp2((v[i].x - m) * kLog2e);
+            v[i].y = fast_exp2((v[i].y - m) * kLog2e);
+            v[i].z = fast_exp2((v[i].z - m) * kLog2e);
+            v[i].w = fast_exp2((v[i].w - m) * kLog2e);
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     }
@@ -265,6 +275,82 @@ rows_staged_kernel(const RowParams p, int stage_bytes) {
     }
 }
 
+// ---- one-shot staged kernel: one bulk copy per CTA, no ring -----------------------------------
+//
+// A CTA owns one contiguous span of the input: kRwWarps * rows_per_stage rows when a warp
+// works on a row (TPR = 32), one row when the whole CTA does (TPR = 256).  Thread 0 issues
+// ONE bulk copy for the span, everybody waits on the same mbarrier and then works from
+// shared memory.  There is no pipeline inside the CTA: overlap comes from the several
+// CTAs resident per SM, and load balance from the block scheduler.
+
+// Registers per thread are capped so that several CTAs stay resident per SM: the bytes
+// in flight per SM are (resident CTAs) x (CTA span), and the row arithmetic is light.
+constexpr int min_ctas_for(int nv) { return nv <= 4 ? 6 : (nv <= 8 ? 4 : 2); }
+
+template <class Op, int TPR, int NV>
+__global__ void __launch_bounds__(kRwThreads, min_ctas_for(NV))
+rows_oneshot_kernel(const RowParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint64_t bar;
+    __shared__ float red[kRwWarps];
+    constexpr int kTeams = kRwThreads / TPR;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int rows_per_cta = kTeams * p.rows_per_stage;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+    int64_t nr = p.rows - r0;
+    if (nr > rows_per_cta) nr = rows_per_cta;
+    const int nvec = p.cols / 4;
+    const size_t row_bytes = static_cast<size_t>(p.cols) * sizeof(float);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        const uint32_t bytes = static_cast<uint32_t>(nr * row_bytes);
+        mbar_expect_tx(&bar, bytes);
+        bulk_g2s(smem, p.x + r0 * p.cols, bytes, &bar);
+    }
+    __syncthreads();  // the barrier is initialised before anyone polls it
+    bool landed = mbar_wait_bounded(&bar, 0);
+    landed = __syncthreads_and(landed);
+    if (!landed) {
+        if (threadIdx.x == 0) atomicOr(p.error_flag, 1u);
+        return;
+    }
+    const float4* src = reinterpret_cast<const float4*>(smem);
+    for (int r = team; r < nr; r += kTeams) {
+        float4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (t + i * TPR < nvec) v[i] = src[r * nvec + t + i * TPR];
+        }
+        row_math<TPR, NV>(Op{}, v, t, nvec, p, r0 + r, red);
+    }
+}
+
+// ---- direct kernel: registers straight from global memory --------------------------------------
+//
+// A team (warp or CTA) per row, all of a row's 128-bit loads issued at once.
+
+template <class Op, int TPR, int NV>
+__global__ void __launch_bounds__(kRwThreads, min_ctas_for(NV))
+rows_direct_kernel(const RowParams p) {
+    __shared__ float red[kRwWarps];
+    constexpr int kTeams = kRwThreads / TPR;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    if (row >= p.rows) return;  // whole teams leave together; a CTA-wide team is the whole CTA
+    const int nvec = p.cols / 4;
+    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (t + i * TPR < nvec) v[i] = ld_stream(src + t + i * TPR);
+    }
+    row_math<TPR, NV>(Op{}, v, t, nvec, p, row, red);
+}
+
 // ---- plain fallback: one CTA per row, three passes ---------------------------------------
 
 template <class Op>
@@ -279,10 +365,10 @@ __global__ void __launch_bounds__(kRwThreads) rows_plain_kernel(const RowParams 
             for (int c = threadIdx.x; c < p.cols; c += kRwThreads) m = fmaxf(m, xr[c]);
             m = team_max<kRwThreads>(m, red);
             float s = 0.0f;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) s += expf(xr[c] - m);
+            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) s += fast_exp2((xr[c] - m) * 1.4426950408889634f);
             s = team_sum<kRwThreads>(s, red);
             const float norm = 1.0f / s;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) yr[c] = expf(xr[c] - m) * norm;
+            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) yr[c] = fast_exp2((xr[c] - m) * 1.4426950408889634f) * norm;
         } else {
             float s = 0.0f;
             for (int c = threadIdx.x; c < p.cols; c += kRwThreads) s += xr[c];
@@ -363,6 +449,54 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
     return launch_status();
 }
 
+template <class Op, int TPR, int NV>
+int launch_oneshot_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t stream) {
+    constexpr int kTeams = kRwThreads / TPR;
+    RowParams q = p;
+    const size_t row_bytes = static_cast<size_t>(p.cols) * sizeof(float);
+    int rps = 1;
+    if (TPR == kWarp && row_bytes < 4096) rps = static_cast<int>(4096 / row_bytes);
+    if (rps > 64) rps = 64;
+    q.rows_per_stage = rps;
+    const size_t smem = static_cast<size_t>(kTeams) * rps * row_bytes;
+    if (smem + 1024 > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
+    auto kernel = rows_oneshot_kernel<Op, TPR, NV>;
+    static size_t configured_smem = 48 * 1024 - 256;
+    if (smem > configured_smem) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured_smem = smem;
+    }
+    int64_t grid = ceil_div(p.rows, static_cast<int64_t>(kTeams) * rps);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    kernel<<<static_cast<unsigned int>(grid), kRwThreads, smem, stream>>>(q);
+    return launch_status();
+}
+
+template <class Op, int TPR, int NV>
+int launch_direct_cfg(const RowParams& p, cudaStream_t stream) {
+    constexpr int kTeams = kRwThreads / TPR;
+    int64_t grid = ceil_div(p.rows, kTeams);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    rows_direct_kernel<Op, TPR, NV><<<static_cast<unsigned int>(grid), kRwThreads, 0, stream>>>(p);
+    return launch_status();
+}
+
+// Picks the team size and registers-per-thread bucket for a row length.
+#define FDL_ROW_DISPATCH(LAUNCH, ...)                                                   \
+    do {                                                                                \
+        const int nvec_ = p.cols / 4;                                                   \
+        if (nvec_ <= 32 * 1) return LAUNCH<Op, kWarp, 1>(__VA_ARGS__);                  \
+        if (nvec_ <= 32 * 2) return LAUNCH<Op, kWarp, 2>(__VA_ARGS__);                  \
+        if (nvec_ <= 32 * 4) return LAUNCH<Op, kWarp, 4>(__VA_ARGS__);                  \
+        if (nvec_ <= 32 * 8) return LAUNCH<Op, kWarp, 8>(__VA_ARGS__);                  \
+        if (nvec_ <= 32 * 16) return LAUNCH<Op, kWarp, 16>(__VA_ARGS__);                \
+        if (nvec_ <= kRwThreads * 4) return LAUNCH<Op, kRwThreads, 4>(__VA_ARGS__);     \
+        if (nvec_ <= kRwThreads * 8) return LAUNCH<Op, kRwThreads, 8>(__VA_ARGS__);     \
+        return LAUNCH<Op, kRwThreads, 16>(__VA_ARGS__);                                 \
+    } while (0)
+
 template <class Op>
 int launch_rows_op(RowParams p, cudaStream_t stream) {
     if (p.rows < 0 || p.cols < 0) return FDL_ERR_INVALID_ARGUMENT;
@@ -378,15 +512,14 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
                         (p.gamma == nullptr || aligned16(p.gamma)) &&
                         (p.beta == nullptr || aligned16(p.beta));
     if (staged) {
-        const int nvec = p.cols / 4;
-        if (nvec <= 32 * 1) return launch_staged_cfg<Op, kWarp, 1>(p, info, stream);
-        if (nvec <= 32 * 2) return launch_staged_cfg<Op, kWarp, 2>(p, info, stream);
-        if (nvec <= 32 * 4) return launch_staged_cfg<Op, kWarp, 4>(p, info, stream);
-        if (nvec <= 32 * 8) return launch_staged_cfg<Op, kWarp, 8>(p, info, stream);
-        if (nvec <= 32 * 16) return launch_staged_cfg<Op, kWarp, 16>(p, info, stream);
-        if (nvec <= kRwThreads * 4) return launch_staged_cfg<Op, kRwThreads, 4>(p, info, stream);
-        if (nvec <= kRwThreads * 8) return launch_staged_cfg<Op, kRwThreads, 8>(p, info, stream);
-        return launch_staged_cfg<Op, kRwThreads, 16>(p, info, stream);
+        switch (tuning().rows_staged) {
+            case 1:
+                FDL_ROW_DISPATCH(launch_staged_cfg, p, info, stream);
+            case 2:
+                FDL_ROW_DISPATCH(launch_oneshot_cfg, p, info, stream);
+            default:
+                FDL_ROW_DISPATCH(launch_direct_cfg, p, stream);
+        }
     }
     const int grid = persistent_grid(info, 8, p.rows);
     rows_plain_kernel<Op><<<grid, kRwThreads, 0, stream>>>(p);

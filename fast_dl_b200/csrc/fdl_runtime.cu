@@ -1,6 +1,7 @@
 // Runtime plumbing of the C ABI: device selection, error text, cached device
 // properties and the library-owned per-device workspace.
 #include <mutex>
+#include <string>
 
 #include "fdl_common.cuh"
 
@@ -21,6 +22,11 @@ struct Workspace {
 Workspace g_workspace[kMaxDevices];
 
 }  // namespace
+
+Tuning& tuning() {
+    static Tuning t;
+    return t;
+}
 
 const DeviceInfo* current_device_info(int* status) {
     int dev = 0;
@@ -106,6 +112,20 @@ const char* fdl_error_string(int status) {
     }
     if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
     return "fdl: unknown status";
+}
+
+int fdl_set_tuning(const char* key, int value) {
+    if (key == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    const std::string k(key);
+    if (k == "sum_cluster" && (value == 1 || value == 2 || value == 4 || value == 8)) {
+        fdl::tuning().sum_cluster = value;
+        return FDL_OK;
+    }
+    if (k == "rows_staged" && value >= 0 && value <= 2) {
+        fdl::tuning().rows_staged = value;
+        return FDL_OK;
+    }
+    return FDL_ERR_INVALID_ARGUMENT;
 }
 
 int fdl_device_count(void) {

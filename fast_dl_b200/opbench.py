@@ -1,0 +1,179 @@
+"""Per-operation bandwidth table for the five workload configurations.
+
+    python -m fast_dl_b200.opbench [--configs c1,c2,c3,c4,c5] [--iters 20] [--reference] [--json out.json]
+
+For every op of every configuration it reports the median launch time (CUDA events around
+each launch; between launches the L2 is flushed by READING a 512 MiB buffer, which leaves
+clean lines behind -- flushing by writing would leave ~100 MB of dirty lines whose
+write-back is then billed to the kernel under test), the algorithmic
+GB/s (compulsory bytes only) and that as a fraction of the measured HBM copy bandwidth.
+With --reference the reference's own CUDA kernels (compiled in place into oracle/_ref by
+oracle/build_ref.py, test infrastructure) are timed on the same buffers as the speed bar.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def peak_gbs() -> float:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"])
+    return 6650.0
+
+
+def main() -> None:
+    import torch
+    from fast_dl_b200 import capi
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--configs", default="c1,c2,c3,c4,c5")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--reference", action="store_true")
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--tune", action="append", default=[], help="key=value passed to fdl_set_tuning")
+    args = ap.parse_args()
+
+    torch.cuda.set_device(0)
+    capi.lib()
+    capi.use_device(0)
+    for kv in args.tune:
+        k, v = kv.split("=")
+        capi.set_tuning(k, int(v))
+    dev = torch.device("cuda", 0)
+    peak = peak_gbs()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(42)
+    ref = None
+    if args.reference:
+        from oracle import ref as _ref
+        if _ref.available():
+            ref = _ref
+
+    def uniform(shape, lo=-1.0, hi=1.0):
+        return torch.empty(shape, dtype=torch.float32, device=dev).uniform_(lo, hi, generator=gen)
+
+    def normal(shape, std=1.0):
+        return torch.empty(shape, dtype=torch.float32, device=dev).normal_(0.0, std, generator=gen)
+
+    results = []
+
+    def timeit(fn, sync_ref=False):
+        times = []
+        for i in range(args.iters + 3):
+            capi.full_sum(flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        return statistics.median(times), min(times)
+
+    def record(config, op, nbytes, fn, ref_fn=None):
+        med, best = timeit(fn)
+        row = {"config": config, "op": op, "bytes": nbytes, "ms": med, "ms_min": best,
+               "GBps": nbytes / med / 1e6, "frac_of_measured_peak": nbytes / med / 1e6 / peak}
+        if ref_fn is not None:
+            rmed, _ = timeit(ref_fn)
+            row["reference_kernel_ms"] = rmed
+            row["reference_kernel_GBps"] = nbytes / rmed / 1e6
+            row["speedup_vs_reference_kernel"] = rmed / med
+        results.append(row)
+        extra = f"  ref {row['reference_kernel_GBps']:8.1f} GB/s  x{row['speedup_vs_reference_kernel']:.2f}" if ref_fn else ""
+        print(f"{config:3s} {op:34s} {med * 1e3:9.1f} us {row['GBps']:8.1f} GB/s  {100 * row['frac_of_measured_peak']:5.1f}%{extra}",
+              flush=True)
+
+    cfgs = args.configs.split(",")
+
+    if "c1" in cfgs:
+        n = 1 << 20
+        a, b, c = uniform(n), uniform(n), uniform(n)
+        out, t1, t2 = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+        record("c1", "fused relu(a*b+c)", 16 * n, lambda: capi.mul_add_relu(a, b, c, out=out))
+
+        def unfused():
+            capi.binary(a, b, capi.MUL, out=t1)
+            capi.binary(t1, c, capi.ADD, out=t2)
+            capi.unary(t2, capi.RELU, out=out)
+
+        def ref_unfused():
+            ref.gpu_elementwise(a.data_ptr(), b.data_ptr(), t1.data_ptr(), n, 2)
+            ref.gpu_elementwise(t1.data_ptr(), c.data_ptr(), t2.data_ptr(), n, 0)
+            ref.gpu_activation(t2.data_ptr(), out.data_ptr(), n, 0)
+
+        record("c1", "unfused mul, add, relu (3 launches)", 32 * n, unfused, ref_unfused if ref else None)
+
+    if "c2" in cfgs:
+        R = C = 4096
+        A, bias, scale = normal((R, C)), normal((1, C)), uniform((R, 1), 0.5, 2.0)
+        out = torch.empty_like(A)
+        nb = 8 * R * C + 4 * C
+        record("c2", "A + b[1,4096]", nb, lambda: capi.broadcast_binary(A, bias, capi.ADD, out=out))
+        record("c2", "A * s[4096,1]", nb, lambda: capi.broadcast_binary(A, scale, capi.MUL, out=out))
+        record("c2", "row bias in place", nb, lambda: capi.add_row_bias_(A, bias.view(-1)),
+               (lambda: ref.gpu_add_row_bias(A.data_ptr(), bias.data_ptr(), R, C)) if ref else None)
+
+    if "c3" in cfgs:
+        R = C = 8192
+        X = normal((R, C))
+        record("c3", "sum axis 1", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_SUM))
+        record("c3", "max axis 1", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_MAX))
+        record("c3", "argmax axis 1 (int64)", 4 * R * C + 8 * R, lambda: capi.argmax_rows(X))
+        record("c3", "mean axis 0", 4 * R * C + 4 * C, lambda: capi.reduce_cols(X, capi.REDUCE_MEAN))
+        record("c3", "full sum", 4 * R * C + 4, lambda: capi.full_sum(X))
+        part = torch.empty(R * C // 1024, dtype=torch.float32, device=dev)
+        record("c3", "1024-block partial sums (address)", 4 * R * C + 4 * R * C // 1024,
+               lambda: capi.block_reduce_1024(X.view(-1), capi.TREE_ADDRESS),
+               (lambda: ref.gpu_reduction(X.data_ptr(), part.data_ptr(), R * C, 1)) if ref else None)
+
+    if "c4" in cfgs:
+        R, C = 65536, 1024
+        L = normal((R, C), 3.0)
+        g, be = uniform(C, 0.9, 1.1), uniform(C, -0.1, 0.1)
+        out = torch.empty_like(L)
+        record("c4", "row softmax", 8 * R * C, lambda: capi.softmax_rows(L, out=out),
+               (lambda: ref.gpu_softmax(L.data_ptr(), out.data_ptr(), R, C, 2)) if ref else None)
+        record("c4", "layernorm", 8 * R * C, lambda: capi.layernorm_rows(L, out=out),
+               (lambda: ref.gpu_layernorm(L.data_ptr(), out.data_ptr(), R, C, 1e-5)) if ref else None)
+        record("c4", "layernorm + gamma, beta", 8 * R * C + 8 * C, lambda: capi.layernorm_rows(L, g, be, out=out))
+        for op, name in ((capi.GELU, "gelu"), (capi.SIGMOID, "sigmoid"), (capi.TANH, "tanh"), (capi.RELU, "relu")):
+            record("c4", f"activation {name}", 8 * R * C, lambda op=op: capi.unary(L, op, out=out),
+                   (lambda op=op: ref.gpu_activation(L.data_ptr(), out.data_ptr(), R * C, op)) if ref else None)
+
+    if "rows" in cfgs:  # extra row-wise shapes: short and long rows
+        for R, C in ((1 << 20, 64), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384)):
+            L = normal((R, C), 3.0)
+            out = torch.empty_like(L)
+            record("row", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
+            record("row", f"layernorm [{R},{C}]", 8 * R * C, lambda: capi.layernorm_rows(L, out=out))
+            del L, out
+
+    if "c5" in cfgs:
+        n, C = 1 << 28, 16384
+        x, y = uniform(n), uniform(n)
+        row = uniform((1, C))
+        out = torch.empty_like(x)
+        record("c5", "binary add", 12 * n, lambda: capi.binary(x, y, capi.ADD, out=out),
+               (lambda: ref.gpu_vector_add(x.data_ptr(), y.data_ptr(), out.data_ptr(), n)) if ref else None)
+        record("c5", "broadcast add [16384,16384]+[1,16384]", 8 * n + 4 * C,
+               lambda: capi.broadcast_binary(x.view(n // C, C), row, capi.ADD, out=out.view(n // C, C)))
+        record("c5", "full sum", 4 * n + 4, lambda: capi.full_sum(x))
+
+    torch.cuda.synchronize()
+    capi.take_device_error()
+    if args.json:
+        Path(args.json).write_text(json.dumps({"peak_gbs": peak, "results": results}, indent=1))
+
+
+if __name__ == "__main__":
+    main()

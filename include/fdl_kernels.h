@@ -88,6 +88,12 @@ int fdl_stream_synchronize(void* stream);
  * after the stream has been synchronised. */
 int fdl_take_device_error(void);
 
+/* Measurement aid: selects a launch shape so that a bench can show, on the same build,
+ * why the default was chosen.  Keys: "sum_cluster" (1, 2, 4 or 8 CTAs per cluster in the
+ * full sum; default 8), "rows_staged" (1 = bulk-async staged softmax/layernorm, 0 = direct
+ * loads; default 1).  Not part of the reference's interface. */
+int fdl_set_tuning(const char* key, int value);
+
 /* ---- elementwise ------------------------------------------------------------------ */
 
 /* out[i] = a[i] (op) b[i], i in [0,n).  IEEE round-to-nearest for all four operators;
