@@ -42,7 +42,7 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // (set through fdl_set_tuning).  Defaults are the measured best on B200.
 struct Tuning {
     int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
-    int rows_staged = 1;   // row softmax/layernorm: 1 = bulk-async ring, 2 = one bulk copy per CTA, 0 = direct loads
+    int rows_staged = 0;   // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA
 };
 Tuning& tuning();
 

@@ -1,18 +1,27 @@
 // Row softmax and row layernorm (fp32), one HBM read and one HBM write per element.
 //
-// Rows are staged into shared memory by the bulk-async copy engine (1-D cp.async.bulk
-// completing on an mbarrier; the non-multicast form, so the same code runs on any number
-// of GPUs).  Each "team" -- one warp for rows up to 2048 floats, one whole CTA for rows up
-// to 16384 floats -- owns a private ring of stages and its own barriers, so in the warp
-// configuration no block-wide barrier is ever executed: a lane-0 thread re-arms a stage as
-// soon as the team has pulled its rows into registers, and the copy engine keeps
-// streaming while the team does its exp / normalise arithmetic and 128-bit stores.
-// A stage holds several consecutive rows when rows are short, so one bulk copy is always
-// a few KiB.  Rows that are unaligned, not a multiple of 4 floats, or longer than 16384
-// floats take a plain three-pass kernel (second and third pass hit L2).
+// A "team" of TPR threads owns a row and keeps it in registers (NV 128-bit packs per
+// thread): 8 or 16 lanes for very short rows, a warp up to 1024 floats, a whole CTA of 256
+// threads up to 8192 floats and of 512 threads up to 16384 floats.  Every CTA handles one
+// fixed group of rows and the hardware block scheduler spreads the CTAs over the SMs.
 //
-// Every mbarrier wait is bounded; when one runs out the team raises a flag in
-// host-visible memory, drains its other stages with bounded waits and leaves.
+// Two ways of bringing a row in are built, selected by fdl_set_tuning("rows_staged", v):
+//   v = 0 (default)  direct: each thread issues all its 128-bit global loads at once;
+//   v = 1            staged: thread 0 issues ONE bulk-async copy (cp.async.bulk on an
+//                    mbarrier, non-multicast) for the CTA's whole span of rows into shared
+//                    memory, and the teams read their rows from there.
+// On B200 the direct form measures 104-107% of the copy-bandwidth yardstick across row
+// lengths 256..16384, the staged form 92-101%, and a persistent per-team ring of bulk
+// copies (removed) 81-90%: with this little arithmetic per byte, enough resident warps
+// already keep the memory system full, and the staged form pays an extra trip through
+// shared memory plus a CTA-wide wait.  The staged form stays selectable so the
+// comparison can be repeated on the same build.
+//
+// Rows that are unaligned, not a multiple of 4 floats, or longer than 16384 floats take a
+// plain three-pass kernel (second and third pass hit L2).
+//
+// The one mbarrier wait is bounded; if it runs out the CTA raises a flag in host-visible
+// memory (fdl_take_device_error) and leaves without touching the output.
 #include <climits>
 #include <cmath>
 #include <type_traits>
@@ -22,10 +31,6 @@
 namespace fdl {
 
 namespace {
-
-constexpr int kRwThreads = 256;
-constexpr int kRwWarps = kRwThreads / kWarp;
-constexpr int kRwStages = 3;
 
 struct SoftmaxOp {};
 struct LayerNormOp {};
@@ -39,48 +44,12 @@ struct RowParams {
     float* rstd_out;     // layernorm only, may be null
     int64_t rows;
     int cols;
-    int rows_per_stage;
+    int rows_per_team;  // staged form: consecutive rows each team takes from the CTA span
     float eps;
     unsigned int* error_flag;  // host-mapped
 };
 
-// ---- team-wide reductions ---------------------------------------------------------------
-
-template <int TPR>
-__device__ __forceinline__ float team_max(float v, float* red) {
-    v = warp_max(v);
-    if (TPR == kWarp) return v;
-    const int lane = threadIdx.x & (kWarp - 1);
-    const int warp = threadIdx.x / kWarp;
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    float r = red[0];
-#pragma unroll
-    for (int k = 1; k < kRwWarps; ++k) r = fmaxf(r, red[k]);
-    __syncthreads();
-    return r;
-}
-
-template <int TPR>
-__device__ __forceinline__ float team_sum(float v, float* red) {
-    v = warp_sum(v);
-    if (TPR == kWarp) return v;
-    const int lane = threadIdx.x & (kWarp - 1);
-    const int warp = threadIdx.x / kWarp;
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    float r = red[0];
-#pragma unroll
-    for (int k = 1; k < kRwWarps; ++k) r += red[k];
-    __syncthreads();
-    return r;
-}
-
-template <int TPR>
-__device__ __forceinline__ void team_sync() {
-    if (TPR == kWarp) __syncwarp();
-    else __syncthreads();
-}
+constexpr int kMaxWarps = 16;
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -88,17 +57,56 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// ---- per-row arithmetic on a register-resident row -----------------------------------------
+// ---- team-wide reductions: TPR <= 32 stays inside a warp, larger teams are the whole CTA ------
 
-template <int TPR, int NV>
+template <int TPR, int TH>
+__device__ __forceinline__ float team_max(float v, float* red) {
+    constexpr int kLanes = TPR < kWarp ? TPR : kWarp;
+#pragma unroll
+    for (int o = kLanes / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+    if (TPR <= kWarp) return v;
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int k = 1; k < TH / kWarp; ++k) r = fmaxf(r, red[k]);
+    __syncthreads();
+    return r;
+}
+
+template <int TPR, int TH>
+__device__ __forceinline__ float team_sum(float v, float* red) {
+    constexpr int kLanes = TPR < kWarp ? TPR : kWarp;
+#pragma unroll
+    for (int o = kLanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+    if (TPR <= kWarp) return v;
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int k = 1; k < TH / kWarp; ++k) r += red[k];
+    __syncthreads();
+    return r;
+}
+
+// ---- per-row arithmetic on a register-resident row -----------------------------------------
+//
+// `active` is false for the lanes of a team that has no row (past the end); they run the
+// same shuffles on neutral values and store nothing.
+
+template <int TPR, int TH, int NV>
 __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int nvec,
-                                         const RowParams& p, int64_t row, float* red) {
+                                         const RowParams& p, int64_t row, bool active, float* red) {
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     }
-    m = team_max<TPR>(m, red);
+    m = team_max<TPR, TH>(m, red);
     // exp(x - m) as 2^((x - m) * log2(e)): the subtraction is the reference's own (exact
     // for the terms that matter, by Sterbenz), then one multiply and one ex2.approx
     // (relative error ~2^-22) instead of the ~9-instruction expf.
@@ -114,7 +122,8 @@ __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int 
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     }
-    s = team_sum<TPR>(s, red);
+    s = team_sum<TPR, TH>(s, red);
+    if (!active) return;
     const float norm = 1.0f / s;
     float4* yr = reinterpret_cast<float4*>(p.y + row * p.cols);
 #pragma unroll
@@ -126,16 +135,16 @@ __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int 
     }
 }
 
-template <int TPR, int NV>
+template <int TPR, int TH, int NV>
 __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, int nvec,
-                                         const RowParams& p, int64_t row, float* red) {
+                                         const RowParams& p, int64_t row, bool active, float* red) {
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
     const float inv_n = 1.0f / static_cast<float>(p.cols);
-    const float mean = team_sum<TPR>(s, red) * inv_n;
+    const float mean = team_sum<TPR, TH>(s, red) * inv_n;
     // Second moment about the mean from the registers: no E[x^2] - E[x]^2 cancellation.
     float q = 0.0f;
 #pragma unroll
@@ -146,7 +155,8 @@ __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, in
             q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
         }
     }
-    const float var = team_sum<TPR>(q, red) * inv_n;
+    const float var = team_sum<TPR, TH>(q, red) * inv_n;
+    if (!active) return;
     const float rstd = 1.0f / sqrtf(var + p.eps);
     if (t == 0) {
         if (p.mean_out != nullptr) p.mean_out[row] = mean;
@@ -174,129 +184,48 @@ __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, in
     }
 }
 
-// ---- the staged kernel ---------------------------------------------------------------------
-//
-// Shared memory: [team][stage] row buffers (stage_bytes each, 128-byte aligned), then
-// [team][stage] mbarriers.  Tile number `tile` covers rows
-// [tile*rows_per_stage, (tile+1)*rows_per_stage) and is one contiguous span of the input.
-
-template <class Op, int TPR, int NV>
-__global__ void __launch_bounds__(kRwThreads)
-rows_staged_kernel(const RowParams p, int stage_bytes) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ float red[kRwWarps];
-    constexpr int kTeams = kRwThreads / TPR;
-    const int team = threadIdx.x / TPR;
-    const int t = threadIdx.x % TPR;
-    unsigned char* my_stages = smem + static_cast<size_t>(team) * kRwStages * stage_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kTeams) * kRwStages * stage_bytes) +
-                     team * kRwStages;
-
-    if (t == 0) {
-#pragma unroll
-        for (int s = 0; s < kRwStages; ++s) mbar_init(bars + s, 1);
-        fence_mbar_init();
-    }
-    __syncthreads();
-
-    const int64_t ntiles = (p.rows + p.rows_per_stage - 1) / p.rows_per_stage;
-    const int64_t team_id = static_cast<int64_t>(blockIdx.x) * kTeams + team;
-    const int64_t team_stride = static_cast<int64_t>(gridDim.x) * kTeams;
-    const int nvec = p.cols / 4;
-    const size_t row_bytes = static_cast<size_t>(p.cols) * sizeof(float);
-
-    auto issue = [&](int64_t tile, int stage) {
-        const int64_t r0 = tile * p.rows_per_stage;
-        int64_t nr = p.rows - r0;
-        if (nr > p.rows_per_stage) nr = p.rows_per_stage;
-        const uint32_t bytes = static_cast<uint32_t>(nr * row_bytes);
-        mbar_expect_tx(bars + stage, bytes);
-        bulk_g2s(my_stages + static_cast<size_t>(stage) * stage_bytes, p.x + r0 * p.cols, bytes,
-                 bars + stage);
-    };
-
-    // Prologue: fill the ring.
-    if (t == 0) {
-#pragma unroll
-        for (int s = 0; s < kRwStages; ++s) {
-            const int64_t tile = team_id + s * team_stride;
-            if (tile < ntiles) issue(tile, s);
-        }
-    }
-
-    int stage = 0;
-    uint32_t parity = 0;
-    bool ok = true;
-    int64_t tile = team_id;
-    for (; tile < ntiles; tile += team_stride) {
-        // The verdict is made uniform across the team so that nobody is left alone at a
-        // later team barrier.
-        bool landed = mbar_wait_bounded(bars + stage, parity);
-        if (TPR == kWarp) landed = __all_sync(kFullMask, landed);
-        else landed = __syncthreads_and(landed);
-        if (!landed) {
-            ok = false;
-            break;
-        }
-        const int64_t r0 = tile * p.rows_per_stage;
-        int nr = p.rows - r0 < p.rows_per_stage ? static_cast<int>(p.rows - r0) : p.rows_per_stage;
-        const float4* src = reinterpret_cast<const float4*>(my_stages + static_cast<size_t>(stage) * stage_bytes);
-        for (int r = 0; r < nr; ++r) {
-            float4 v[NV];
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                if (t + i * TPR < nvec) v[i] = src[r * nvec + t + i * TPR];
-            }
-            if (r == nr - 1) {
-                // The stage is now entirely in registers: hand it back to the copy engine.
-                team_sync<TPR>();
-                const int64_t next = tile + kRwStages * team_stride;
-                if (t == 0 && next < ntiles) issue(next, stage);
-            }
-            row_math<TPR, NV>(Op{}, v, t, nvec, p, r0 + r, red);
-        }
-        if (++stage == kRwStages) {
-            stage = 0;
-            parity ^= 1u;
-        }
-    }
-
-    if (!ok) {
-        if (t == 0) atomicOr(p.error_flag, 1u);
-        // Give copies that may still be in flight a bounded chance to land before the
-        // shared memory is released.
-        for (int k = 0; k < kRwStages; ++k) {
-            if (tile + k * team_stride < ntiles) mbar_wait_bounded(bars + stage, parity);
-            if (++stage == kRwStages) {
-                stage = 0;
-                parity ^= 1u;
-            }
-        }
-    }
+// Registers per thread are capped so that several CTAs stay resident per SM: the bytes in
+// flight per SM are (resident CTAs) x (bytes a CTA requests), and the arithmetic is light.
+constexpr int min_ctas_for(int th, int nv) {
+    return th > 256 ? (nv <= 4 ? 3 : 2) : (nv <= 4 ? 6 : (nv <= 8 ? 4 : 2));
 }
 
-// ---- one-shot staged kernel: one bulk copy per CTA, no ring -----------------------------------
-//
-// A CTA owns one contiguous span of the input: kRwWarps * rows_per_stage rows when a warp
-// works on a row (TPR = 32), one row when the whole CTA does (TPR = 256).  Thread 0 issues
-// ONE bulk copy for the span, everybody waits on the same mbarrier and then works from
-// shared memory.  There is no pipeline inside the CTA: overlap comes from the several
-// CTAs resident per SM, and load balance from the block scheduler.
+// ---- direct form ----------------------------------------------------------------------------------
 
-// Registers per thread are capped so that several CTAs stay resident per SM: the bytes
-// in flight per SM are (resident CTAs) x (CTA span), and the row arithmetic is light.
-constexpr int min_ctas_for(int nv) { return nv <= 4 ? 6 : (nv <= 8 ? 4 : 2); }
-
-template <class Op, int TPR, int NV>
-__global__ void __launch_bounds__(kRwThreads, min_ctas_for(NV))
-rows_oneshot_kernel(const RowParams p) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ uint64_t bar;
-    __shared__ float red[kRwWarps];
-    constexpr int kTeams = kRwThreads / TPR;
+template <class Op, int TPR, int TH, int NV>
+__global__ void __launch_bounds__(TH, min_ctas_for(TH, NV))
+rows_direct_kernel(const RowParams p) {
+    __shared__ float red[kMaxWarps];
+    constexpr int kTeams = TH / TPR;
     const int team = threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
-    const int rows_per_cta = kTeams * p.rows_per_stage;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    const bool active = row < p.rows;
+    if (TPR >= kWarp && !active) return;  // whole warps / the whole CTA leave together
+    const int nvec = p.cols / 4;
+    const float4* src = reinterpret_cast<const float4*>(p.x + (active ? row : 0) * p.cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (t + i * TPR < nvec) {
+            v[i] = active ? ld_stream(src + t + i * TPR) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, row, active, red);
+}
+
+// ---- staged form: one bulk copy per CTA ---------------------------------------------------------
+
+template <class Op, int TPR, int TH, int NV>
+__global__ void __launch_bounds__(TH, min_ctas_for(TH, NV))
+rows_staged_kernel(const RowParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint64_t bar;
+    __shared__ float red[kMaxWarps];
+    constexpr int kTeams = TH / TPR;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int rows_per_cta = kTeams * p.rows_per_team;
     const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
     int64_t nr = p.rows - r0;
     if (nr > rows_per_cta) nr = rows_per_cta;
@@ -318,74 +247,64 @@ rows_oneshot_kernel(const RowParams p) {
         return;
     }
     const float4* src = reinterpret_cast<const float4*>(smem);
-    for (int r = team; r < nr; r += kTeams) {
+    // Team k takes rows k, k + kTeams, ... of the span; the trip count is the same for all
+    // teams of a warp, so sub-warp teams shuffle together.
+    for (int i0 = 0; i0 < p.rows_per_team; ++i0) {
+        const int r = i0 * kTeams + team;
+        const bool active = r < nr;
+        if (TPR >= kWarp && !active) break;
         float4 v[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            if (t + i * TPR < nvec) v[i] = src[r * nvec + t + i * TPR];
+            if (t + i * TPR < nvec) {
+                v[i] = active ? src[r * nvec + t + i * TPR] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
-        row_math<TPR, NV>(Op{}, v, t, nvec, p, r0 + r, red);
+        row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, r0 + r, active, red);
     }
-}
-
-// ---- direct kernel: registers straight from global memory --------------------------------------
-//
-// A team (warp or CTA) per row, all of a row's 128-bit loads issued at once.
-
-template <class Op, int TPR, int NV>
-__global__ void __launch_bounds__(kRwThreads, min_ctas_for(NV))
-rows_direct_kernel(const RowParams p) {
-    __shared__ float red[kRwWarps];
-    constexpr int kTeams = kRwThreads / TPR;
-    const int team = threadIdx.x / TPR;
-    const int t = threadIdx.x % TPR;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
-    if (row >= p.rows) return;  // whole teams leave together; a CTA-wide team is the whole CTA
-    const int nvec = p.cols / 4;
-    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols);
-    float4 v[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (t + i * TPR < nvec) v[i] = ld_stream(src + t + i * TPR);
-    }
-    row_math<TPR, NV>(Op{}, v, t, nvec, p, row, red);
 }
 
 // ---- plain fallback: one CTA per row, three passes ---------------------------------------
 
+constexpr int kPlainThreads = 256;
+
 template <class Op>
-__global__ void __launch_bounds__(kRwThreads) rows_plain_kernel(const RowParams p) {
-    __shared__ float red[kRwWarps];
+__global__ void __launch_bounds__(kPlainThreads) rows_plain_kernel(const RowParams p) {
+    __shared__ float red[kMaxWarps];
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr int T = kPlainThreads;
+    constexpr float kLog2e = 1.4426950408889634f;
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const float* xr = p.x + row * p.cols;
         float* yr = p.y + row * p.cols;
         if (kSoftmax) {
             float m = -INFINITY;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) m = fmaxf(m, xr[c]);
-            m = team_max<kRwThreads>(m, red);
+            for (int c = threadIdx.x; c < p.cols; c += T) m = fmaxf(m, xr[c]);
+            m = team_max<T, T>(m, red);
             float s = 0.0f;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) s += fast_exp2((xr[c] - m) * 1.4426950408889634f);
-            s = team_sum<kRwThreads>(s, red);
+            for (int c = threadIdx.x; c < p.cols; c += T) s += fast_exp2((xr[c] - m) * kLog2e);
+            s = team_sum<T, T>(s, red);
             const float norm = 1.0f / s;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) yr[c] = fast_exp2((xr[c] - m) * 1.4426950408889634f) * norm;
+            for (int c = threadIdx.x; c < p.cols; c += T) {
+                yr[c] = fast_exp2((xr[c] - m) * kLog2e) * norm;
+            }
         } else {
             float s = 0.0f;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) s += xr[c];
+            for (int c = threadIdx.x; c < p.cols; c += T) s += xr[c];
             const float inv_n = 1.0f / static_cast<float>(p.cols);
-            const float mean = team_sum<kRwThreads>(s, red) * inv_n;
+            const float mean = team_sum<T, T>(s, red) * inv_n;
             float q = 0.0f;
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) {
+            for (int c = threadIdx.x; c < p.cols; c += T) {
                 const float d = xr[c] - mean;
                 q += d * d;
             }
-            const float var = team_sum<kRwThreads>(q, red) * inv_n;
+            const float var = team_sum<T, T>(q, red) * inv_n;
             const float rstd = 1.0f / sqrtf(var + p.eps);
             if (threadIdx.x == 0) {
                 if (p.mean_out != nullptr) p.mean_out[row] = mean;
                 if (p.rstd_out != nullptr) p.rstd_out[row] = rstd;
             }
-            for (int c = threadIdx.x; c < p.cols; c += kRwThreads) {
+            for (int c = threadIdx.x; c < p.cols; c += T) {
                 float o = (xr[c] - mean) * rstd;
                 if (p.gamma != nullptr) o *= p.gamma[c];
                 if (p.beta != nullptr) o += p.beta[c];
@@ -414,23 +333,30 @@ int error_flag_device_ptr(unsigned int** dev) {
     return FDL_OK;
 }
 
-template <class Op, int TPR, int NV>
+template <class Op, int TPR, int TH, int NV>
+int launch_direct_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream) {
+    constexpr int kTeams = TH / TPR;
+    const int64_t grid = ceil_div(p.rows, kTeams);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    rows_direct_kernel<Op, TPR, TH, NV><<<static_cast<unsigned int>(grid), TH, 0, stream>>>(p);
+    return launch_status();
+}
+
+template <class Op, int TPR, int TH, int NV>
 int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t stream) {
-    constexpr int kTeams = kRwThreads / TPR;
+    constexpr int kTeams = TH / TPR;
     RowParams q = p;
     const size_t row_bytes = static_cast<size_t>(p.cols) * sizeof(float);
-    // Short rows share a stage so that one bulk copy moves about 4 KiB.
-    int rps = 1;
-    if (TPR == kWarp && row_bytes < 4096) rps = static_cast<int>(4096 / row_bytes);
-    if (rps > 64) rps = 64;
-    q.rows_per_stage = rps;
-    size_t stage_bytes = rps * row_bytes;
-    stage_bytes = (stage_bytes + 127) / 128 * 128;
-    const size_t smem = kTeams * kRwStages * (stage_bytes + sizeof(uint64_t));
+    // Short rows: each team takes several consecutive rows so that a CTA's one bulk copy
+    // moves about 32 KiB.
+    int rpt = 1;
+    if (kTeams * row_bytes < 32768) rpt = static_cast<int>(32768 / (kTeams * row_bytes));
+    if (rpt > 64) rpt = 64;
+    q.rows_per_team = rpt;
+    const size_t smem = static_cast<size_t>(kTeams) * rpt * row_bytes;
     if (smem + 1024 > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
-
-    auto kernel = rows_staged_kernel<Op, TPR, NV>;
-    static size_t configured_smem = 0;
+    auto kernel = rows_staged_kernel<Op, TPR, TH, NV>;
+    static size_t configured_smem = 48 * 1024 - 256;
     if (smem > configured_smem) {
         // Exactly what is needed: the opt-in ceiling covers static + dynamic together.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -438,63 +364,26 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
         if (e != cudaSuccess) return static_cast<int>(e);
         configured_smem = smem;
     }
-    int blocks_per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel,
-                                                                  kRwThreads, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    if (blocks_per_sm < 1) return FDL_ERR_UNSUPPORTED;
-    const int64_t ntiles = ceil_div(p.rows, rps);
-    const int grid = persistent_grid(info, blocks_per_sm, ceil_div(ntiles, kTeams));
-    kernel<<<grid, kRwThreads, smem, stream>>>(q, static_cast<int>(stage_bytes));
-    return launch_status();
-}
-
-template <class Op, int TPR, int NV>
-int launch_oneshot_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t stream) {
-    constexpr int kTeams = kRwThreads / TPR;
-    RowParams q = p;
-    const size_t row_bytes = static_cast<size_t>(p.cols) * sizeof(float);
-    int rps = 1;
-    if (TPR == kWarp && row_bytes < 4096) rps = static_cast<int>(4096 / row_bytes);
-    if (rps > 64) rps = 64;
-    q.rows_per_stage = rps;
-    const size_t smem = static_cast<size_t>(kTeams) * rps * row_bytes;
-    if (smem + 1024 > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
-    auto kernel = rows_oneshot_kernel<Op, TPR, NV>;
-    static size_t configured_smem = 48 * 1024 - 256;
-    if (smem > configured_smem) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured_smem = smem;
-    }
-    int64_t grid = ceil_div(p.rows, static_cast<int64_t>(kTeams) * rps);
+    const int64_t grid = ceil_div(p.rows, static_cast<int64_t>(kTeams) * rpt);
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
-    kernel<<<static_cast<unsigned int>(grid), kRwThreads, smem, stream>>>(q);
+    kernel<<<static_cast<unsigned int>(grid), TH, smem, stream>>>(q);
     return launch_status();
 }
 
-template <class Op, int TPR, int NV>
-int launch_direct_cfg(const RowParams& p, cudaStream_t stream) {
-    constexpr int kTeams = kRwThreads / TPR;
-    int64_t grid = ceil_div(p.rows, kTeams);
-    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
-    rows_direct_kernel<Op, TPR, NV><<<static_cast<unsigned int>(grid), kRwThreads, 0, stream>>>(p);
-    return launch_status();
-}
-
-// Picks the team size and registers-per-thread bucket for a row length.
-#define FDL_ROW_DISPATCH(LAUNCH, ...)                                                   \
-    do {                                                                                \
-        const int nvec_ = p.cols / 4;                                                   \
-        if (nvec_ <= 32 * 1) return LAUNCH<Op, kWarp, 1>(__VA_ARGS__);                  \
-        if (nvec_ <= 32 * 2) return LAUNCH<Op, kWarp, 2>(__VA_ARGS__);                  \
-        if (nvec_ <= 32 * 4) return LAUNCH<Op, kWarp, 4>(__VA_ARGS__);                  \
-        if (nvec_ <= 32 * 8) return LAUNCH<Op, kWarp, 8>(__VA_ARGS__);                  \
-        if (nvec_ <= 32 * 16) return LAUNCH<Op, kWarp, 16>(__VA_ARGS__);                \
-        if (nvec_ <= kRwThreads * 4) return LAUNCH<Op, kRwThreads, 4>(__VA_ARGS__);     \
-        if (nvec_ <= kRwThreads * 8) return LAUNCH<Op, kRwThreads, 8>(__VA_ARGS__);     \
-        return LAUNCH<Op, kRwThreads, 16>(__VA_ARGS__);                                 \
+// Picks the team size and the registers-per-thread bucket for a row length.
+#define FDL_ROW_DISPATCH(LAUNCH)                                                         \
+    do {                                                                                 \
+        const int nvec_ = p.cols / 4;                                                    \
+        if (nvec_ <= 8) return LAUNCH<Op, 8, 256, 1>(p, info, stream);                   \
+        if (nvec_ <= 16) return LAUNCH<Op, 16, 256, 1>(p, info, stream);                 \
+        if (nvec_ <= 32) return LAUNCH<Op, 32, 256, 1>(p, info, stream);                 \
+        if (nvec_ <= 64) return LAUNCH<Op, 32, 256, 2>(p, info, stream);                 \
+        if (nvec_ <= 128) return LAUNCH<Op, 32, 256, 4>(p, info, stream);                \
+        if (nvec_ <= 256) return LAUNCH<Op, 32, 256, 8>(p, info, stream);                \
+        if (nvec_ <= 512) return LAUNCH<Op, 256, 256, 2>(p, info, stream);               \
+        if (nvec_ <= 1024) return LAUNCH<Op, 256, 256, 4>(p, info, stream);              \
+        if (nvec_ <= 2048) return LAUNCH<Op, 256, 256, 8>(p, info, stream);              \
+        return LAUNCH<Op, 512, 512, 8>(p, info, stream);                                 \
     } while (0)
 
 template <class Op>
@@ -508,21 +397,16 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     status = error_flag_device_ptr(&p.error_flag);
     if (status != FDL_OK) return status;
 
-    const bool staged = p.cols % 4 == 0 && p.cols <= 16384 && aligned16(p.x) && aligned16(p.y) &&
-                        (p.gamma == nullptr || aligned16(p.gamma)) &&
-                        (p.beta == nullptr || aligned16(p.beta));
-    if (staged) {
-        switch (tuning().rows_staged) {
-            case 1:
-                FDL_ROW_DISPATCH(launch_staged_cfg, p, info, stream);
-            case 2:
-                FDL_ROW_DISPATCH(launch_oneshot_cfg, p, info, stream);
-            default:
-                FDL_ROW_DISPATCH(launch_direct_cfg, p, stream);
-        }
+    const bool in_registers = p.cols % 4 == 0 && p.cols <= 16384 && aligned16(p.x) &&
+                              aligned16(p.y) && (p.gamma == nullptr || aligned16(p.gamma)) &&
+                              (p.beta == nullptr || aligned16(p.beta));
+    if (in_registers) {
+        if (tuning().rows_staged != 0) FDL_ROW_DISPATCH(launch_staged_cfg);
+        FDL_ROW_DISPATCH(launch_direct_cfg);
     }
-    const int grid = persistent_grid(info, 8, p.rows);
-    rows_plain_kernel<Op><<<grid, kRwThreads, 0, stream>>>(p);
+    int64_t grid = p.rows;
+    if (grid > 2147483647) grid = 2147483647;
+    rows_plain_kernel<Op><<<static_cast<unsigned int>(grid), kPlainThreads, 0, stream>>>(p);
     return launch_status();
 }
 

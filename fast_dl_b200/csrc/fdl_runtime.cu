@@ -121,7 +121,7 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().sum_cluster = value;
         return FDL_OK;
     }
-    if (k == "rows_staged" && value >= 0 && value <= 2) {
+    if (k == "rows_staged" && (value == 0 || value == 1)) {
         fdl::tuning().rows_staged = value;
         return FDL_OK;
     }

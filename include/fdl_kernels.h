@@ -90,8 +90,9 @@ int fdl_take_device_error(void);
 
 /* Measurement aid: selects a launch shape so that a bench can show, on the same build,
  * why the default was chosen.  Keys: "sum_cluster" (1, 2, 4 or 8 CTAs per cluster in the
- * full sum; default 8), "rows_staged" (1 = bulk-async staged softmax/layernorm, 0 = direct
- * loads; default 1).  Not part of the reference's interface. */
+ * full sum; default 4), "rows_staged" (0 = softmax/layernorm rows loaded straight into
+ * registers, 1 = staged through shared memory by one bulk-async copy per CTA; default 0).
+ * Not part of the reference's interface. */
 int fdl_set_tuning(const char* key, int value);
 
 /* ---- elementwise ------------------------------------------------------------------ */
