@@ -42,6 +42,9 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // (set through fdl_set_tuning).  Defaults are the measured best on B200.
 struct Tuning {
     int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
+    int cols_tx = 64;            // column reduction: threads across columns per CTA (16..256)
+    int cols_cluster = 4;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8)
+    int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
     int rows_staged = 0;   // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA
 };
 Tuning& tuning();

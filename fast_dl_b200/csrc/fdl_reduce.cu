@@ -312,6 +312,7 @@ int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsig
 // ======================================================================================
 
 struct SumRed {
+    static constexpr bool kIsArgmax = false;
     using State = float;
     using Out = float;
     __device__ static State identity() { return 0.0f; }
@@ -324,6 +325,7 @@ struct MeanRed : SumRed {
     __device__ static Out finish(State a, int64_t, float divisor) { return a / divisor; }
 };
 struct MaxRed {
+    static constexpr bool kIsArgmax = false;
     using State = float;
     using Out = float;
     __device__ static State identity() { return -INFINITY; }
@@ -337,6 +339,7 @@ struct ArgState {
     int i;
 };
 struct ArgmaxRed {
+    static constexpr bool kIsArgmax = true;
     using State = ArgState;
     using Out = int64_t;
     __device__ static State identity() { return ArgState{-INFINITY, INT_MAX}; }
@@ -356,7 +359,7 @@ struct ArgmaxRed {
 };
 
 constexpr int kRowThreads = 256;
-constexpr int kRowUnroll = 4;
+constexpr int kRowUnroll = 4;  // independent accumulator chains per thread
 
 // TPR threads cooperate on a row (32: one warp per row, 8 rows per CTA; 256: one CTA per
 // row).  W = 4 needs cols % 4 == 0 and a 16-byte aligned base.
@@ -379,7 +382,44 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
 #pragma unroll
         for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
         int p = t;
-        if (W == 4) {
+        if (R::kIsArgmax && W == 4) {
+            // Argmax works on whole packs: three fmaxf (which skip NaNs) and one compare per
+            // 128-bit load.  Only when a pack beats the running maximum -- rare once a few
+            // packs have been seen -- is the winning lane inside it worked out.
+            const float4* xv = reinterpret_cast<const float4*>(xr);
+            float best[kRowUnroll];
+            int best_col[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                best[u] = -INFINITY;
+                best_col[u] = INT_MAX;
+            }
+            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
+                float4 v[kRowUnroll];
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * TPR);
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) {
+                    const float m4 = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
+                    if (m4 > best[u]) {
+                        best[u] = m4;
+                        best_col[u] = (p + u * TPR) * 4 +
+                                      (v[u].x == m4 ? 0 : (v[u].y == m4 ? 1 : (v[u].z == m4 ? 2 : 3)));
+                    }
+                }
+            }
+            for (; p < npack; p += TPR) {
+                const float4 v = ld_stream(xv + p);
+                const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                if (m4 > best[0]) {
+                    best[0] = m4;
+                    best_col[0] = p * 4 + (v.x == m4 ? 0 : (v.y == m4 ? 1 : (v.z == m4 ? 2 : 3)));
+                }
+            }
+            // Chains hold disjoint, interleaved column sets: ties go to the lower column.
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::lift(best[u], best_col[u]);
+        } else if (W == 4) {
             const float4* xv = reinterpret_cast<const float4*>(xr);
             for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
                 float4 v[kRowUnroll];
@@ -487,7 +527,7 @@ struct ColMax {
     __device__ static float combine(float a, float b) { return fmaxf(a, b); }
 };
 
-template <class R, int W>
+template <class R, int W, int CL>
 __global__ void __launch_bounds__(kColThreads)
 reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float* partials,
                    unsigned int* counters, int tx, int rows_per_chunk, float scale) {
@@ -502,10 +542,11 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     const int64_t b = blockIdx.z;
     const float* xb = x + b * rows * cols;
 
-    constexpr int kInFlight = 4;  // rows in flight per thread
-    float acc[kInFlight][W];
+    constexpr int kInFlight = 8;  // rows in flight per thread: 32 KiB requested per CTA at a time
+    constexpr int kAcc = 2;
+    float acc[kAcc][W];
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
+    for (int u = 0; u < kAcc; ++u) {
 #pragma unroll
         for (int k = 0; k < W; ++k) acc[u][k] = R::identity();
     }
@@ -531,7 +572,7 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
 #pragma unroll
             for (int u = 0; u < kInFlight; ++u) {
 #pragma unroll
-                for (int k = 0; k < W; ++k) acc[u][k] = R::combine(acc[u][k], v[u][k]);
+                for (int k = 0; k < W; ++k) acc[u % kAcc][k] = R::combine(acc[u % kAcc][k], v[u][k]);
             }
         }
         for (; r < r_end; r += ty_count) {
@@ -548,39 +589,79 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     const int tile_w = tx * W;
 #pragma unroll
     for (int k = 0; k < W; ++k) {
-        tile[ry * tile_w + cx * W + k] =
-            R::combine(R::combine(acc[0][k], acc[1][k]), R::combine(acc[2][k], acc[3][k]));
+        tile[ry * tile_w + cx * W + k] = R::combine(acc[0][k], acc[1][k]);
     }
     __syncthreads();
 
-    // Fold the TY rows of the tile (fixed order) -- threads 0..tile_w-1 own one column each.
-    float* dst = nchunks == 1 ? out + b * cols
-                              : partials + (static_cast<int64_t>(chunk) * gridDim.z + b) * cols;
+    // Fold the TY rows of the tile (fixed order): thread c owns column c and leaves the
+    // CTA's value for it in tile[c].
     const int64_t col0 = static_cast<int64_t>(blockIdx.x) * tile_w;
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
         float s = tile[c];
         for (int y = 1; y < ty_count; ++y) s = R::combine(s, tile[y * tile_w + c]);
-        if (col0 + c < cols) dst[col0 + c] = nchunks == 1 ? s * scale : s;
+        tile[c] = s;
     }
-    if (nchunks == 1) return;
 
-    __threadfence();
+    // Cluster stage: the CL CTAs of a cluster hold consecutive row chunks of the same
+    // columns; the leader reads the others' values through distributed shared memory and
+    // folds them in rank order.
+    int groups = nchunks;
+    int group = chunk;
+    if (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();  // every CTA's tile[0..tile_w) is final (and every CTA is running)
+        const unsigned int rank = cluster.block_rank();
+        if (rank == 0) {
+            for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
+                float s = tile[c];
+#pragma unroll
+                for (int k = 1; k < CL; ++k) s = R::combine(s, cluster.map_shared_rank(tile, k)[c]);
+                tile[c] = s;
+            }
+        }
+        cluster.sync();  // peers stay resident until the leader has read them
+        if (rank != 0) return;
+        groups = nchunks / CL;
+        group = chunk / CL;
+    }
+
+    float* dst = groups == 1 ? out + b * cols
+                             : partials + (static_cast<int64_t>(group) * gridDim.z + b) * cols;
+    for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
+        if (col0 + c < cols) dst[col0 + c] = groups == 1 ? tile[c] * scale : tile[c];
+    }
+    if (groups == 1) return;
+
+    // The CTA barrier orders every thread's partial stores before thread 0's fence, and
+    // fences are cumulative, so one device-scope fence publishes the whole CTA's partials
+    // (a fence in every thread costs a memory-barrier stall per CTA wave).
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();
         unsigned int* ctr = counters + b * gridDim.x + blockIdx.x;
         const unsigned int ticket = atomicAdd(ctr, 1u);
-        is_last = ticket == static_cast<unsigned int>(nchunks - 1);
+        is_last = ticket == static_cast<unsigned int>(groups - 1);
         if (is_last) *ctr = 0;
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // The last group to arrive folds all group partials of its columns in group order;
+    // loads are issued eight at a time so their latencies overlap.
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
         if (col0 + c >= cols) continue;
+        const float* src = partials + b * cols + col0 + c;
+        const int64_t stride = static_cast<int64_t>(gridDim.z) * cols;
         float s = R::identity();
-        for (int k = 0; k < nchunks; ++k) {
-            s = R::combine(s, __ldcg(partials + (static_cast<int64_t>(k) * gridDim.z + b) * cols + col0 + c));
+        int k = 0;
+        for (; k + 8 <= groups; k += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (k + j) * stride);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = R::combine(s, v[j]);
         }
+        for (; k < groups; ++k) s = R::combine(s, __ldcg(src + k * stride));
         out[b * cols + col0 + c] = s * scale;
     }
 }
@@ -589,7 +670,8 @@ struct ColsGeometry {
     int tx;              // threads across columns (power of two, <= 256)
     int w;               // floats per thread (4 or 1)
     int col_blocks;      // gridDim.x
-    int chunks;          // gridDim.y
+    int chunks;          // gridDim.y (a multiple of `cluster`)
+    int cluster;         // CTAs per cluster along the chunk dimension (1 or kColCluster)
     int rows_per_chunk;
     size_t counter_bytes;
     size_t scratch_bytes;
@@ -600,27 +682,37 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     g->w = vec ? 4 : 1;
     const int64_t packs = ceil_div(cols, g->w);
     int tx = 1;
-    while (tx < 64 && tx < packs) tx <<= 1;  // up to 64 threads = 1 KiB of a row per CTA
+    const int tx_max = tuning().cols_tx;  // threads across columns (x4 floats = row bytes per CTA)
+    while (tx < tx_max && tx < packs) tx <<= 1;
     g->tx = tx;
     g->col_blocks = static_cast<int>(ceil_div(packs, tx));
     const int ty = kColThreads / tx;
     // Many more CTAs than SMs (the block scheduler balances them), but at least 16 rows
     // per thread in a chunk so that partials stay a small fraction of the traffic.
-    const int64_t target = static_cast<int64_t>(sm_count) * 32;
+    const int64_t target = static_cast<int64_t>(sm_count) * tuning().cols_ctas_per_sm;
     int64_t chunks = ceil_div(target, static_cast<int64_t>(g->col_blocks) * batch);
-    const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 16);
+    const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 32);
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks < 1) chunks = 1;
     if (chunks > 65535) chunks = 65535;
     g->rows_per_chunk = static_cast<int>(ceil_div(rows, chunks));
     g->chunks = static_cast<int>(ceil_div(rows, g->rows_per_chunk));
+    g->cluster = 1;
+    const int want_cluster = tuning().cols_cluster;
+    if (want_cluster > 1 && g->chunks >= want_cluster) {
+        // Round up to whole clusters; trailing chunks may be empty (they contribute the
+        // identity).
+        g->cluster = want_cluster;
+        g->chunks = static_cast<int>(ceil_div(g->chunks, want_cluster)) * want_cluster;
+    }
+    const int groups = g->chunks / g->cluster;
     const size_t ncounters = static_cast<size_t>(g->col_blocks) * batch;
     g->counter_bytes = ((ncounters * sizeof(unsigned int) + 255) / 256) * 256;
     g->scratch_bytes =
-        g->chunks == 1
+        groups == 1
             ? 0
             : g->counter_bytes +
-                  ((static_cast<size_t>(g->chunks) * batch * cols * sizeof(float) + 255) / 256) * 256;
+                  ((static_cast<size_t>(groups) * batch * cols * sizeof(float) + 255) / 256) * 256;
     return FDL_OK;
 }
 
@@ -751,7 +843,7 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
     cols_geometry(info->sm_count, batch, rows, cols, vec, &g);
     float* partials = nullptr;
     unsigned int* counters = nullptr;
-    if (g.chunks > 1) {
+    if (g.chunks / g.cluster > 1) {
         if (scratch == nullptr) {
             status = get_workspace(g.scratch_bytes, &scratch);
             if (status != FDL_OK) return status;
@@ -763,16 +855,37 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
         partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + g.counter_bytes);
     }
     const float scale = op == FDL_REDUCE_MEAN ? static_cast<float>(1.0 / mean_divisor) : 1.0f;
-    const dim3 grid(g.col_blocks, g.chunks, static_cast<unsigned int>(batch));
-    const size_t smem = static_cast<size_t>(kColThreads) * g.w * sizeof(float);
-    cudaStream_t s = as_stream(stream);
-    if (op == FDL_REDUCE_MAX) {
-        if (vec) reduce_cols_kernel<ColMax, 4><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
-        else reduce_cols_kernel<ColMax, 1><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
-    } else {
-        if (vec) reduce_cols_kernel<ColSum, 4><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
-        else reduce_cols_kernel<ColSum, 1><<<grid, kColThreads, smem, s>>>(x, rows, cols, out, partials, counters, g.tx, g.rows_per_chunk, scale);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(g.col_blocks, g.chunks, static_cast<unsigned int>(batch));
+    cfg.blockDim = dim3(kColThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(kColThreads) * g.w * sizeof(float);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = g.cluster;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g.cluster > 1 ? 1 : 0;
+    const bool is_max = op == FDL_REDUCE_MAX;
+    cudaError_t e;
+#define FDL_LAUNCH_COLS(R, W, CL)                                                              \
+    e = cudaLaunchKernelEx(&cfg, reduce_cols_kernel<R, W, CL>, x, rows, cols, out, partials,  \
+                           counters, g.tx, g.rows_per_chunk, scale)
+#define FDL_LAUNCH_COLS_CL(CL)                                                                  \
+    do {                                                                                        \
+        if (is_max) { if (vec) FDL_LAUNCH_COLS(ColMax, 4, CL); else FDL_LAUNCH_COLS(ColMax, 1, CL); } \
+        else { if (vec) FDL_LAUNCH_COLS(ColSum, 4, CL); else FDL_LAUNCH_COLS(ColSum, 1, CL); }  \
+    } while (0)
+    switch (g.cluster) {
+        case 8: FDL_LAUNCH_COLS_CL(8); break;
+        case 4: FDL_LAUNCH_COLS_CL(4); break;
+        case 2: FDL_LAUNCH_COLS_CL(2); break;
+        default: FDL_LAUNCH_COLS_CL(1); break;
     }
+#undef FDL_LAUNCH_COLS_CL
+#undef FDL_LAUNCH_COLS
+    if (e != cudaSuccess) return static_cast<int>(e);
     return launch_status();
 }
 

@@ -121,6 +121,18 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().sum_cluster = value;
         return FDL_OK;
     }
+    if (k == "cols_tx" && (value == 16 || value == 32 || value == 64 || value == 128 || value == 256)) {
+        fdl::tuning().cols_tx = value;
+        return FDL_OK;
+    }
+    if (k == "cols_cluster" && (value == 1 || value == 2 || value == 4 || value == 8)) {
+        fdl::tuning().cols_cluster = value;
+        return FDL_OK;
+    }
+    if (k == "cols_ctas_per_sm" && value >= 1 && value <= 256) {
+        fdl::tuning().cols_ctas_per_sm = value;
+        return FDL_OK;
+    }
     if (k == "rows_staged" && (value == 0 || value == 1)) {
         fdl::tuning().rows_staged = value;
         return FDL_OK;
