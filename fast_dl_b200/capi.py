@@ -40,6 +40,7 @@ PROTOTYPES = {
     "fdl_sum_scratch_bytes": (_sz, [_i64]),
     "fdl_reduce_cols_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "fdl_sum_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "fdl_sum_f32_static": (_int, [_vp, _i64, _vp, _vp, _vp]),
     "fdl_reduce_rows_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
     "fdl_argmax_rows_f32": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "fdl_reduce_cols_f32": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f64, _vp, _sz, _vp]),
@@ -210,6 +211,17 @@ def full_sum(x, want_f64=False, scratch=None):
     check(lib().fdl_sum_f32(_ptr(x), x.numel(), _ptr(out), _ptr(out64), _ptr(scratch),
                             0 if scratch is None else scratch.numel() * scratch.element_size(),
                             _stream()), "fdl_sum_f32")
+    return (out, out64) if want_f64 else out
+
+
+def full_sum_static(x, want_f64=False):
+    """fdl_sum_f32_static: the full sum with its scratch in the library's fixed device array."""
+    import torch
+    _require(x, torch.float32)
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    out64 = torch.empty(1, dtype=torch.float64, device=x.device) if want_f64 else None
+    check(lib().fdl_sum_f32_static(_ptr(x), x.numel(), _ptr(out), _ptr(out64), _stream()),
+          "fdl_sum_f32_static")
     return (out, out64) if want_f64 else out
 
 

@@ -9,6 +9,7 @@
 #include <cooperative_groups.h>
 
 #include <cfloat>
+#include <mutex>
 #include <climits>
 #include <cmath>
 
@@ -791,6 +792,54 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void
         default:
             return launch_sum<8, true>(x, n, out_f32, out_f64, counter, partials, s);
     }
+}
+
+// ---- full sum for callers that must not allocate ------------------------------------------------
+//
+// The scratch of the full sum (arrival counter + per-cluster partials) lives in a fixed
+// array in device memory that is part of the library image: every GPU that loads the
+// library carries these 65,792 bytes until the process exits.  In host code the array's name
+// is only a handle for the runtime, not a device address; the address each device uses is
+// asked for once, with that device current, through cudaGetSymbolAddress.
+
+// Same layout and size as the scratch the regular entry point asks for: the kernel never
+// writes more than kSumMaxPartials partials whatever n is (CTAs loop over tiles beyond
+// that).  The element count is nevertheless capped at a stated maximum.
+constexpr int64_t kStaticSumMaxElems = int64_t{1} << 30;
+static __device__ __align__(256) unsigned char g_static_sum_scratch[kCounterBytes + kSumMaxPartials * sizeof(double)];
+
+static std::mutex g_static_mutex;
+static void* g_static_sum_ptr[64] = {};
+
+int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f64, void* stream) {
+    if (n < 0 || (out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
+    if (n > 0 && x == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    if (n > kStaticSumMaxElems) return FDL_ERR_TOO_LARGE_FOR_STATIC_SCRATCH;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= 64) return FDL_ERR_NO_DEVICE;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (g_static_sum_ptr[dev] == nullptr) {
+            // Set-up, once per device, with that device current.
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_static_sum_scratch);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            g_static_sum_ptr[dev] = ptr;
+        }
+        scratch = g_static_sum_ptr[dev];
+    }
+    cudaStream_t s = as_stream(stream);
+    // The array keeps whatever the previous call left: the arrival counter must start at 0.
+    e = cudaMemsetAsync(scratch, 0, kCounterBytes, s);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    unsigned int* counter = static_cast<unsigned int*>(scratch);
+    double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
+    // Fixed launch shape (clusters of 4): at most kSumMaxPartials partials are written.
+    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s);
+    return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s);
 }
 
 int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,

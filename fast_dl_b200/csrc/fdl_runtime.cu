@@ -107,6 +107,8 @@ const char* fdl_error_string(int status) {
             return "fdl: a bounded device-side wait ran out";
         case FDL_ERR_NO_DEVICE:
             return "fdl: no usable CUDA device";
+        case FDL_ERR_TOO_LARGE_FOR_STATIC_SCRATCH:
+            return "fdl: element count exceeds the 2^30 maximum of the static-scratch entry point";
         default:
             break;
     }

@@ -38,6 +38,7 @@ extern "C" {
 #define FDL_ERR_WORKSPACE (-3)        /* caller-provided scratch too small or misaligned */
 #define FDL_ERR_DEVICE_WAIT (-4)      /* a bounded device-side wait ran out              */
 #define FDL_ERR_NO_DEVICE (-5)        /* no usable CUDA device / driver                  */
+#define FDL_ERR_TOO_LARGE_FOR_STATIC_SCRATCH (-6) /* n above fdl_sum_f32_static's maximum */
 
 /* Binary operator selector; numeric values equal dl::kernels::ElementwiseOp
  * (include/dl/kernels/elementwise.hpp:7-12). */
@@ -168,6 +169,25 @@ size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols);
  * (src/kernels/cuda/reduction.cu:34-57). */
 int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64,
                 void* scratch, size_t scratch_bytes, void* stream);
+
+/* Full sum for callers that cannot allocate device memory: a host framework whose own
+ * allocator must account for every device byte, a service whose device-memory budget is
+ * fixed at start-up, or latency-critical code that must not enter the driver's allocator
+ * (cudaMalloc and cudaFree synchronise the device).  Same result as fdl_sum_f32, but the scratch is a fixed 65,792-byte
+ * array in the library's device image instead of caller- or library-allocated memory, and
+ * the call performs no cudaMalloc/cudaFree or any other allocating routine.
+ *   - n may be at most 2^30 (1,073,741,824) elements; larger n returns
+ *     FDL_ERR_TOO_LARGE_FOR_STATIC_SCRATCH without launching anything.
+ *   - The first call on each device looks the array's device address up (one
+ *     cudaGetSymbolAddress with that device current); make that first call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array: the arrival counter in it is cleared on
+ *     the stream at the start of every call, and two calls whose kernels may overlap on
+ *     the GPU (different streams without an ordering between them) race on it.  Serialise
+ *     them, or use fdl_sum_f32 with separate scratch buffers.
+ * This entry point has no counterpart in the reference. */
+int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f64,
+                       void* stream);
 
 /* Row-wise reduction of a row-major [rows, cols] matrix along axis 1:
  * out[r] = op over c of x[r, c]; FDL_REDUCE_MAX ignores NaNs like fmaxf.  No counterpart
