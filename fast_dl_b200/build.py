@@ -102,6 +102,12 @@ def build_core(force: bool = False) -> Path | None:
         _run(["g++", "-shared", "-o", str(out), *map(str, objects),
               "-L", str(LIB), "-lfdl_kernels", "-Wl,-rpath,$ORIGIN",
               "-L", str(cuda_home / "lib64"), "-lcudart_static", "-lcublas", "-ldl", "-lrt", "-lpthread"])
+    # The host library's own test programs (run on a GPU box by the test suite).
+    for src in sorted((HOST / "tests").glob("*.cpp")):
+        exe = LIB / src.stem
+        if force or _newer(exe, [src, out] + headers):
+            _run(["g++", "-O1", "-std=c++17", "-I", str(HOST / "include"), "-I", str(cuda_home / "include"),
+                  str(src), "-o", str(exe), "-L", str(LIB), "-ldl_core", "-lfdl_kernels", "-Wl,-rpath,$ORIGIN"])
     return out
 
 

@@ -46,6 +46,10 @@ PROTOTYPES = {
     "fdl_reduce_cols_f32": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f64, _vp, _sz, _vp]),
     "fdl_softmax_rows_f32": (_int, [_vp, _vp, _i64, _i64, _vp]),
     "fdl_layernorm_rows_f32": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp]),
+    "fdl_cross_entropy_f32": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "fdl_transpose_f32": (_int, [_vp, _vp, _i64, _vp]),
+    "fdl_uniform_f32": (_int, [_vp, _i64, _f32, _f32, C.c_uint64, _vp]),
+    "fdl_normal_f32": (_int, [_vp, _i64, _f32, _f32, C.c_uint64, _vp]),
     "fdl_host_binary_f32": (_int, [_vp, _vp, _vp, _i64, _int]),
     "fdl_host_unary_f32": (_int, [_vp, _vp, _i64, _int, _f32]),
     "fdl_host_mul_add_relu_f32": (_int, [_vp, _vp, _vp, _vp, _i64]),

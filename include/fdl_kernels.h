@@ -228,6 +228,28 @@ int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta
                            float* y, float* mean_out, float* rstd_out, int64_t rows,
                            int64_t cols, float eps, void* stream);
 
+/* ---- neighbours of the path (needed to stand in for the whole kernel library) ------------ */
+
+/* loss[0] = mean over rows of (log sum_c exp(logits[r,c]) - logits[r,label[r]]); rows whose
+ * label is outside [0, classes) contribute 0.  Deterministic (no float atomics).  Replaces
+ * dl::kernels::cross_entropy (include/dl/kernels/cross_entropy.hpp:7-8,
+ * src/kernels/cuda/cross_entropy.cu:9-43). */
+int fdl_cross_entropy_f32(const float* logits, const int64_t* labels, float* loss,
+                          int64_t batch, int64_t classes, void* stream);
+
+/* out = transpose of the square row-major matrix in[n, n] (out must not alias in).
+ * Replaces dl::kernels::transpose (include/dl/kernels/transpose.hpp:15-16,
+ * src/kernels/cuda/transpose.cu:7-111), all three algorithm values. */
+int fdl_transpose_f32(const float* in, float* out, int64_t n, void* stream);
+
+/* data[i] uniform in (low, high] / normal(mean, stddev), a pure function of (seed, i)
+ * (Philox4x32-10; the reference's per-element XORWOW sequence is not reproduced -- its
+ * tests require only same-seed repeatability and the range).  Replace
+ * dl::kernels::uniform_float32 / normal_float32 (include/dl/kernels/random.hpp:7-8,
+ * src/kernels/cuda/random.cu:7-56). */
+int fdl_uniform_f32(float* data, int64_t n, float low, float high, uint64_t seed, void* stream);
+int fdl_normal_f32(float* data, int64_t n, float mean, float stddev, uint64_t seed, void* stream);
+
 /* ---- host-buffer entry points ---------------------------------------------------------- */
 
 /* The same operations with HOST pointers (`h_*`): the library moves the data through a

@@ -1,0 +1,39 @@
+"""The C++ host library on a GPU: the reference's own 17 test programs, compiled unmodified
+against this repository's `dl::` headers and libraries (oracle/build_ref.py), and the host
+library's own test program for the API additions (fast_dl_b200/host/tests)."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+REF_TESTS = ROOT / "oracle" / "_ref" / "tests"
+pytestmark = pytest.mark.gpu
+
+REFERENCE_PROGRAMS = [
+    "test_tensor", "tensor_copy_test", "tensor_uniform_test", "tensor_randn_test", "elementwise_tensor_test",
+    "activation_tensor_test", "softmax_tensor_test", "layernorm_tensor_test", "matmul_tensor_test",
+    "linear_tensor_test", "cross_entropy_tensor_test", "relu_module_test", "linear_module_test",
+    "sequential_module_test", "custom_module_test", "linear_init_test", "linear_kaiming_init_test",
+]
+
+
+def run(exe):
+    return subprocess.run([str(exe)], capture_output=True, text=True, timeout=120, cwd=str(ROOT))
+
+
+@pytest.mark.parametrize("name", REFERENCE_PROGRAMS)
+def test_reference_program_passes_against_this_library(cuda, name):
+    exe = REF_TESTS / name
+    if not exe.exists():
+        pytest.skip("oracle/_ref/tests was not built (needs the reference tree at build time)")
+    proc = run(exe)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "not passed" not in proc.stdout and "passed" in proc.stdout, proc.stdout
+
+
+def test_host_library_additions(cuda):
+    exe = ROOT / "fast_dl_b200" / "lib" / "host_ops_test"
+    assert exe.exists(), "run python -m fast_dl_b200.build core"
+    proc = run(exe)
+    assert proc.returncode == 0 and "not passed" not in proc.stdout, proc.stdout + proc.stderr
