@@ -1,25 +1,28 @@
 #!/usr/bin/env python
 """Bench of the fast_dl tensor hot path on B200: effective GB/s and fraction of the HBM roofline.
 
-Workload: the large-tensor sweep (268,435,456 fp32 elements, uniform [-1, 1]) -- one "step" is
-    1. c = a + b                                   (12 B/element)
-    2. e = view(d, [16384, 16384]) + row[1, 16384] ( 8 B/element + the row)
-    3. s = sum(f)  (+ all-reduce of the per-GPU partials when N > 1)   (4 B/element)
+Workload (BASELINE.json config 5): the large-tensor sweep over 268,435,456 fp32 elements,
+uniform [-1, 1], viewed as [16384, 16384].  One "step" is
+    z = x + y                 binary add                       12 B/element
+    w = x + row[1, 16384]     broadcast add against a row       8 B/element (+ the row)
+    s = sum(x)                full sum (+ all-reduce of the per-GPU partials when N > 1)   4 B/element
 The tensors are partitioned along the leading dimension over the N ranks (one process per
-GPU; row vector replicated), so total work is fixed as N grows ("strong" scaling).  The six
-tensors are distinct, so every step streams 6 x (1 GiB / N) per GPU: far more than the L2.
+GPU, row vector replicated), so total work is fixed as N grows ("strong" scaling).  In the
+device-resident leg every operand is a DISTINCT tensor, so each step streams 6 x (1 GiB / N)
+per GPU -- far more than the L2; in the end-to-end leg x and y are host tensors.
 
     python bench.py [--gpus N] [--steps K] [--warmup W]          # this repository's CUDA path
     python bench.py --impl reference [...]                       # the reference's CPU code on the host cores
 
-Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic GB/s with inputs resident in
-HBM; `e2e` is the same metric through the host-buffer C-ABI entry points, host<->device copies
-inside the timed region; `roofline` describes the dominant kernel (the binary add);
-`cpu_baseline` is the reference's CPU code timed on this box's host cores.
+Prints ONE JSON line (rank 0).  `value`: whole-job algorithmic GB/s, inputs resident in HBM.
+`e2e`: the same metric through the host-buffer C-ABI entry point (pinned host tensors in,
+results in host memory, copies inside the timed region).  `roofline`: the dominant kernel
+(the binary add).  `cpu_baseline`: the reference's CPU code on this box's host cores.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 import sys
@@ -35,6 +38,7 @@ N_ELEMS = 268_435_456
 COLS = 16_384
 ROWS = N_ELEMS // COLS
 METRIC = "effective_GBps_large_tensor_sweep"
+WORKLOAD = "large_tensor_sweep_268435456_f32: z=x+y, w=x+row[1,16384], s=sum(x)"
 
 
 def algorithmic_bytes(rows: int, cols: int) -> dict:
@@ -55,11 +59,12 @@ def measured_peak_gbs() -> tuple[float, str]:
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.01):
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
+        self._nv = None
 
     def start(self):
         try:
@@ -105,26 +110,30 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------
 # CPU side: the reference's own CPU code (oracle/_ref) where it has some, the oracle port else.
+# Only this leg (cpu_baseline / --impl reference) touches oracle/.
 # ---------------------------------------------------------------------------------------------
 
+def _fptr(arr, offset_elems=0):
+    return C.cast(arr.ctypes.data + 4 * offset_elems, C.POINTER(C.c_float))
+
+
 class CpuPath:
-    """One step of the sweep on the host cores, over `rows` rows of the [ROWS, COLS] view."""
+    """One step of the sweep on the host cores over `rows` rows of the [ROWS, COLS] view."""
 
     def __init__(self, threads: int | None = None):
         from oracle import oracle as orc
         from oracle import ref
-        self.orc, self.ref = orc, ref
+        self.lib, self.ref = orc.lib(), ref
         self.have_ref = ref.available()
         self.threads = threads or os.cpu_count() or 1
         self.pool = ThreadPoolExecutor(self.threads)
-        orc.lib()
 
     @property
     def kind(self) -> str:
         return "reference" if self.have_ref else "port"
 
     def describe(self) -> str:
-        add = ("vector_add_cpu of the reference (tests/benchmarks/vector_add/vector_add_benchmark.cu:13-18)"
+        add = ("the reference's vector_add_cpu (tests/benchmarks/vector_add/vector_add_benchmark.cu:13-18)"
                if self.have_ref else "oracle port of the reference's vector_add_cpu")
         return (f"add: {add}; broadcast add and full sum: oracle port (the reference has no such op); "
                 f"rows split over {self.threads} threads")
@@ -133,90 +142,75 @@ class CpuPath:
         per = -(-rows // self.threads)
         return [(lo, min(rows, lo + per)) for lo in range(0, rows, per)]
 
-    def step(self, a, b, c, row, rows: int) -> float:
-        """a, b, c: numpy float32 [rows*COLS]; returns the sum (float)."""
-        import numpy as np
-        orc, ref = self.orc, self.ref
-        parts = self._split(rows)
+    def step(self, x, y, z, w, row, rows: int) -> float:
+        """x, y, z, w: numpy float32 of at least rows*COLS elements; returns sum(x)."""
+        lib, parts = self.lib, self._split(rows)
+        n = rows * COLS
         if self.have_ref:
-            ref.cpu_vector_add(a[:rows * COLS], b[:rows * COLS], threads=self.threads, out=c)
+            self.ref.cpu_vector_add(x[:n], y[:n], threads=self.threads, out=z)
         else:
-            list(self.pool.map(lambda p: orc.lib().orc_binary_f32(
-                _fptr(a, p[0] * COLS), _fptr(b, p[0] * COLS), _fptr(c, p[0] * COLS),
-                _i64((p[1] - p[0]) * COLS), 0), parts))
-        # row-broadcast add: the reference's row-bias arithmetic (src/kernels/cuda/bias.cu:5-12), in place on c
-        list(self.pool.map(lambda p: orc.lib().orc_add_row_bias_f32(
-            _fptr(c, p[0] * COLS), _fptr(row, 0), _i64(p[1] - p[0]), _i64(COLS), 0), parts))
-        sums = list(self.pool.map(lambda p: orc.lib().orc_sum_f64(
-            _fptr(b, p[0] * COLS), _i64((p[1] - p[0]) * COLS)), parts))
-        return float(np.sum(np.asarray(sums, dtype=np.float64)))
-
-
-def _fptr(arr, offset_elems):
-    import ctypes as C
-    return C.cast(arr.ctypes.data + 4 * offset_elems, C.POINTER(C.c_float))
-
-
-def _i64(v):
-    import ctypes as C
-    return C.c_int64(v)
+            list(self.pool.map(lambda p: lib.orc_binary_f32(
+                _fptr(x, p[0] * COLS), _fptr(y, p[0] * COLS), _fptr(z, p[0] * COLS),
+                C.c_int64((p[1] - p[0]) * COLS), 0), parts))
+        list(self.pool.map(lambda p: lib.orc_add_row_f32(
+            _fptr(x, p[0] * COLS), _fptr(row), _fptr(w, p[0] * COLS), C.c_int64(p[1] - p[0]), C.c_int64(COLS)), parts))
+        sums = list(self.pool.map(lambda p: lib.orc_sum_f64(
+            _fptr(x, p[0] * COLS), C.c_int64((p[1] - p[0]) * COLS)), parts))
+        return float(sum(sums))
 
 
 def time_cpu(cpu: CpuPath, host, rows: int, steps: int, warmup: int) -> float:
     """Seconds per step of the CPU path over `rows` rows."""
-    a, b, c, row = host
     for _ in range(warmup):
-        cpu.step(a, b, c, row, rows)
+        cpu.step(*host, rows)
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu.step(a, b, c, row, rows)
+        cpu.step(*host, rows)
     return (time.perf_counter() - t0) / steps
 
 
 def host_inputs(rows: int, seed: int, pinned: bool):
-    """Seeded uniform[-1,1] host tensors for `rows` rows (torch CPU tensors + numpy views)."""
+    """Seeded uniform[-1,1] host tensors x, y (inputs), z, w (results), row, for `rows` rows."""
     import torch
     g = torch.Generator().manual_seed(seed)
     n = rows * COLS
 
-    def mk(count):
+    def mk(count, fill=True):
         t = torch.empty(count, dtype=torch.float32, pin_memory=pinned)
-        t.uniform_(-1.0, 1.0, generator=g)
+        if fill:
+            t.uniform_(-1.0, 1.0, generator=g)
+        else:
+            t.zero_()  # touch the pages
         return t
 
-    return mk(n), mk(n), torch.empty(n, dtype=torch.float32, pin_memory=pinned), mk(COLS)
+    return mk(n), mk(n), mk(n, False), mk(n, False), mk(COLS)
 
 
 # ---------------------------------------------------------------------------------------------
-# reference arm
+# reference arm: the reference's CPU implementation of the path on the host cores
 # ---------------------------------------------------------------------------------------------
 
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     cpu = CpuPath()
     # Bounded sample: as many leading rows as keep the whole run within ~2 minutes.
     probe_rows = ROWS // 64
-    host = host_inputs(probe_rows, 42, pinned=False)
-    np_host = tuple(t.numpy() for t in host)
-    t_probe = time_cpu(cpu, np_host, probe_rows, steps=2, warmup=1)
+    host = tuple(t.numpy() for t in host_inputs(probe_rows, 42, pinned=False))
+    t_probe = time_cpu(cpu, host, probe_rows, steps=2, warmup=1)
     budget = 120.0 / max(1, args.steps + args.warmup)
     rows = int(min(ROWS, max(probe_rows, probe_rows * budget / max(t_probe, 1e-9))))
     rows = max(64, rows // 64 * 64)
     if rows != probe_rows:
-        host = host_inputs(rows, 42, pinned=False)
-        np_host = tuple(t.numpy() for t in host)
-    sec = time_cpu(cpu, np_host, rows, args.steps, args.warmup)
-    nbytes = sum(algorithmic_bytes(rows, COLS).values())
-    gbs = nbytes / sec / 1e9
+        host = tuple(t.numpy() for t in host_inputs(rows, 42, pinned=False))
+    sec = time_cpu(cpu, host, rows, args.steps, args.warmup)
+    gbs = sum(algorithmic_bytes(rows, COLS).values()) / sec / 1e9
     sample = f"{rows} of {ROWS} rows of the [16384,16384] view per step ({rows * COLS} elements); " + cpu.describe()
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "large_tensor_sweep_268435456_f32: add, row-broadcast add, full sum",
-                   "l2": "inputs larger than L2"},
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -228,17 +222,29 @@ def run_reference(args) -> None:
 # this repository's CUDA path
 # ---------------------------------------------------------------------------------------------
 
+def traffic_per_launch(algorithmic: int):
+    """DRAM bytes per launch of the add kernel from the committed ncu capture, scaled by size."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if not p.exists():
+        return None
+    try:
+        rec = json.loads(p.read_text())["map_kernel_add"]
+        return rec["dram_bytes"] / rec["algorithmic_bytes"] * algorithmic
+    except Exception:
+        return None
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
     from fast_dl_b200 import capi
+    from fast_dl_b200.sharding import shard_rows
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("launch with `python -m torch.distributed.run --nproc-per-node N bench.py --gpus N`")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
@@ -247,15 +253,15 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    total_rows = args.rows
-    rows = total_rows // world + (1 if rank < total_rows % world else 0)
-    n = rows * COLS
+    shard = shard_rows(args.rows, world, rank)
+    rows, n = shard.count, shard.count * COLS
     dev = torch.device("cuda", local)
     gen = torch.Generator(device=dev).manual_seed(42 + rank)
 
     def uni(count):
         return torch.empty(count, dtype=torch.float32, device=dev).uniform_(-1.0, 1.0, generator=gen)
 
+    # Six distinct tensors per step so that nothing is L2-resident from the previous op.
     a, b, d, f = uni(n), uni(n), uni(n), uni(n)
     c, e = torch.empty_like(a), torch.empty_like(a)
     row = uni(COLS)
@@ -263,8 +269,9 @@ def run_ours(args) -> None:
         dist.broadcast(row, 0)
     sum32 = torch.zeros(1, dtype=torch.float32, device=dev)
     sum64 = torch.zeros(1, dtype=torch.float64, device=dev)
-    d2 = d.view(rows, COLS)
-    e2 = e.view(rows, COLS)
+    d2, e2, row2 = d.view(rows, COLS), e.view(rows, COLS), row.view(1, COLS)
+    stream = torch.cuda.current_stream().cuda_stream
+    lib = capi.lib()
 
     def step(events=None):
         if events is not None:
@@ -272,22 +279,23 @@ def run_ours(args) -> None:
         capi.binary(a, b, capi.ADD, out=c)
         if events is not None:
             events[1].record()
-        capi.broadcast_binary(d2, row.view(1, COLS), capi.ADD, out=e2)
+        capi.broadcast_binary(d2, row2, capi.ADD, out=e2)
         if events is not None:
             events[2].record()
-        capi.check(capi.lib().fdl_sum_f32(f.data_ptr(), n, sum32.data_ptr(), sum64.data_ptr(), None, 0,
-                                          torch.cuda.current_stream().cuda_stream), "fdl_sum_f32")
+        capi.check(lib.fdl_sum_f32(f.data_ptr(), n, sum32.data_ptr(), sum64.data_ptr(), None, 0, stream),
+                   "fdl_sum_f32")
         if events is not None:
             events[3].record()
         if world > 1:
-            dist.all_reduce(sum64)  # per-GPU partials -> global sum, on the same stream
+            dist.all_reduce(sum64)  # per-GPU partials -> global sum: same stream, no host round trip
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier()
 
@@ -307,26 +315,28 @@ def run_ours(args) -> None:
     ms_total = start.elapsed_time(stop)
     per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)) / K for i in range(3)]
 
-    # ---- end to end through the host-buffer entry points ------------------------------------------
+    # ---- end to end: host tensors in, host results out, through the C ABI ------------------------
     need_host = not args.no_e2e or (rank == 0 and world == 1 and not args.no_cpu)
-    ha = hb = hc = hrow = ha2 = hc2 = None
+    host = None
+    e2e_steps, e2e_sec = 0, float("nan")
     if need_host:
-        ha, hb, hc, hrow = host_inputs(rows, 1000 + rank, pinned=True)
-        ha2, hc2 = ha.view(rows, COLS), hc.view(rows, COLS)
+        del c, e, d, f
+        torch.cuda.empty_cache()
+        host = host_inputs(rows, 1000 + rank, pinned=True)
+    if not args.no_e2e:
+        hx, hy, hz, hw, hrow = host
+        hx2, hy2, hz2, hw2 = (t.view(rows, COLS) for t in (hx, hy, hz, hw))
+        tsum = torch.zeros(1, dtype=torch.float64, device=dev)
 
-    def e2e_step():
-        capi.host_binary(ha, hb, hc, capi.ADD)
-        capi.host_row_broadcast(ha2, hrow, hc2, capi.ADD)
-        s = capi.host_sum(hb)
-        if world > 1:
-            t = torch.tensor([s], dtype=torch.float64, device=dev)
-            dist.all_reduce(t)
-            s = float(t.item())
-        return s
+        def e2e_step():
+            s = capi.host_sweep(hx2, hy2, hrow, hz2, hw2)
+            if world > 1:
+                tsum.fill_(s)
+                dist.all_reduce(tsum)
+                s = float(tsum.item())
+            return s
 
-    e2e_steps = 0 if args.no_e2e else max(2, min(5, K))
-    e2e_sec = float("nan")
-    if e2e_steps:
+        e2e_steps = max(2, min(5, K))
         e2e_step()
         barrier()
         t0 = time.perf_counter()
@@ -335,50 +345,49 @@ def run_ours(args) -> None:
         barrier()
         e2e_sec = (time.perf_counter() - t0) / e2e_steps
 
-    # ---- reduce over ranks ------------------------------------------------------------------------------
-    stats = torch.tensor([ms_total, e2e_sec, *per_op], dtype=torch.float64, device=dev)
+    # ---- reduce over ranks: the slowest rank defines the time --------------------------------------
+    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     ms_total, e2e_sec, t_add, t_bc, t_sum = stats.tolist()
 
-    total_bytes = sum(algorithmic_bytes(total_rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
+    total_bytes = sum(algorithmic_bytes(args.rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
     value = total_bytes * K / (ms_total * 1e-3) / 1e9
-    e2e_value = total_bytes / e2e_sec / 1e9
     peak, peak_kind = measured_peak_gbs()
-    shard = algorithmic_bytes(rows, COLS)
-    achieved = shard["add"] / (t_add * 1e-3) / 1e9
+    big = algorithmic_bytes(shard_rows(args.rows, world, 0).count, COLS)  # rank 0 holds a largest shard
+    achieved = big["add"] / (t_add * 1e-3) / 1e9
+
+    def op_line(name, t):
+        gbs = big[name] / t / 1e6
+        return {"ms": t, "GBps": gbs, "frac": gbs / peak}
 
     line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": warmup,
         "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "large_tensor_sweep_268435456_f32: add, row-broadcast add, full sum",
-                   "partition": f"leading dimension over {world} GPU(s), {rows} of {total_rows} rows on rank 0",
+        "config": {"workload": WORKLOAD,
+                   "partition": f"leading dimension over {world} GPU(s): {rows} of {args.rows} rows on rank 0",
                    "l2": "inputs larger than L2 (six distinct tensors stream per step)"},
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "GB/s",
-                "h2d_bytes_per_step": (4 * n + COLS) * 4 * world, "d2h_bytes_per_step": (2 * n * 4 + 8) * world,
-                "steps": e2e_steps},
+        "e2e": {"value": (total_bytes / e2e_sec / 1e9) if e2e_steps else None, "unit": "GB/s",
+                "h2d_bytes_per_step": (2 * args.rows * COLS + world * COLS) * 4,
+                "d2h_bytes_per_step": 2 * args.rows * COLS * 4 + 8 * world, "steps": e2e_steps,
+                "api": "fdl_host_sweep_f32 (pinned host tensors in, host results out)"},
         "gpu_launches": 3 * K * world,
-        "roofline": {"bound": "hbm", "kernel": "map_kernel<4,2,AddFn> (binary add)", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": "map_kernel<4,2,4,AddFn> (binary add)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "traffic": traffic_per_launch(shard["add"])},
-        "per_op": {
-            "add": {"ms": t_add, "GBps": shard["add"] / t_add / 1e6, "frac": shard["add"] / t_add / 1e6 / peak},
-            "broadcast_add": {"ms": t_bc, "GBps": shard["broadcast_add"] / t_bc / 1e6,
-                              "frac": shard["broadcast_add"] / t_bc / 1e6 / peak},
-            "sum": {"ms": t_sum, "GBps": shard["sum"] / t_sum / 1e6, "frac": shard["sum"] / t_sum / 1e6 / peak},
-        },
+                     "traffic": traffic_per_launch(big["add"])},
+        "per_op": {"add": op_line("add", t_add), "broadcast_add": op_line("broadcast_add", t_bc),
+                   "sum": op_line("sum", t_sum)},
     }
-
     if args.rows != ROWS:
-        line["config"]["workload"] += f" (REDUCED to {args.rows} rows for profiling; not a bench value)"
+        line["config"]["workload"] += f" (REDUCED to {args.rows} rows for a profiler capture; not a bench value)"
+
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
             cpu = CpuPath()
             sample_rows = min(ROWS // 4, rows)
-            np_host = (ha.numpy(), hb.numpy(), hc.numpy(), hrow.numpy())
-            sec = time_cpu(cpu, np_host, sample_rows, steps=3, warmup=1)
+            sec = time_cpu(cpu, tuple(t.numpy() for t in host), sample_rows, steps=3, warmup=1)
             nb = sum(algorithmic_bytes(sample_rows, COLS).values())
             line["cpu_baseline"] = {
                 "value": nb / sec / 1e9, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind,
@@ -391,18 +400,6 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
-
-
-def traffic_per_launch(algorithmic: int):
-    """DRAM bytes per launch of the add kernel from the committed ncu capture, scaled by size."""
-    p = ROOT / "profiles" / "dram_traffic.json"
-    if not p.exists():
-        return None
-    try:
-        rec = json.loads(p.read_text())["map_kernel_add"]
-        return rec["dram_bytes"] / rec["algorithmic_bytes"] * algorithmic
-    except Exception:
-        return None
 
 
 def main() -> None:

@@ -55,6 +55,7 @@ PROTOTYPES = {
     "fdl_host_mul_add_relu_f32": (_int, [_vp, _vp, _vp, _vp, _i64]),
     "fdl_host_row_broadcast_f32": (_int, [_vp, _vp, _vp, _i64, _i64, _int]),
     "fdl_host_sum_f32": (_int, [_vp, _i64, C.POINTER(C.c_double)]),
+    "fdl_host_sweep_f32": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, C.POINTER(C.c_double)]),
 }
 
 
@@ -319,4 +320,13 @@ def host_row_broadcast(a, row, out, op):
 def host_sum(x) -> float:
     res = C.c_double(0.0)
     check(lib().fdl_host_sum_f32(_ptr(x), x.numel(), C.byref(res)), "fdl_host_sum_f32")
+    return res.value
+
+
+def host_sweep(x, y, row, z, w) -> float:
+    """z = x + y, w = x + row, returns sum(x); x, y, z, w are [rows, cols] host tensors."""
+    rows, cols = x.shape
+    res = C.c_double(0.0)
+    check(lib().fdl_host_sweep_f32(_ptr(x), _ptr(y), _ptr(row), _ptr(z), _ptr(w), rows, cols, C.byref(res)),
+          "fdl_host_sweep_f32")
     return res.value

@@ -258,7 +258,7 @@ int fdl_normal_f32(float* data, int64_t n, float mean, float stddev, uint64_t se
  * reference's Tensor::from_host -> dl::ops::<op> -> Tensor::to_host round trip
  * (include/dl/tensor/Tensor.hpp:97-121, src/tensor/TensorImpl.cpp:91-125) for callers
  * whose tensors live on the host.  Buffers should be page-locked (pageable memory works
- * but serialises the copies).  Staging memory (4 slots x 96 MiB per device) is allocated
+ * but serialises the copies).  Staging memory (4 slots x 128 MiB per device) is allocated
  * on first use and kept. */
 int fdl_host_binary_f32(const float* h_a, const float* h_b, float* h_out, int64_t n, int op);
 int fdl_host_unary_f32(const float* h_x, float* h_out, int64_t n, int op, float alpha);
@@ -269,6 +269,12 @@ int fdl_host_row_broadcast_f32(const float* h_a, const float* h_row, float* h_ou
                                int64_t rows, int64_t cols, int op);
 /* *h_out = sum of h_x[0..n) (double; chunk partials folded on the host in order). */
 int fdl_host_sum_f32(const float* h_x, int64_t n, double* h_out);
+/* Three results from one pass over host data x, y of shape [rows, cols] and row[cols]:
+ * z = x + y, w = x + row (row broadcast over the rows), *h_sum = sum(x).  Each chunk of x
+ * and y is uploaded once and feeds all three kernels, so the link carries 2 tensors up and
+ * 2 down instead of 4 up and 2 down for three separate calls. */
+int fdl_host_sweep_f32(const float* h_x, const float* h_y, const float* h_row, float* h_z,
+                       float* h_w, int64_t rows, int64_t cols, double* h_sum);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -93,6 +93,14 @@ void orc_add_row_bias_f32(float* out, const float* bias, int64_t rows, int64_t c
     }
 }
 
+/* out[r, c] = x[r, c] + row[c], out of place: the row-bias arithmetic of
+ * src/kernels/cuda/bias.cu:5-12 written to a separate result. */
+void orc_add_row_f32(const float* x, const float* row, float* out, int64_t rows, int64_t cols) {
+    int64_t r, c;
+    for (r = 0; r < rows; ++r)
+        for (c = 0; c < cols; ++c) out[r * cols + c] = x[r * cols + c] + row[c];
+}
+
 /* ---- general broadcast binary (not in fast_dl; NumPy semantics): the elementwise IEEE
  * op on the broadcast-expanded operands.  Strides in elements, 0 = broadcast. ---- */
 void orc_broadcast_binary_f32(const float* a, const float* b, float* out, int ndim,
