@@ -269,6 +269,14 @@ def run_ours(args) -> None:
         dist.broadcast(row, 0)
     sum32 = torch.zeros(1, dtype=torch.float32, device=dev)
     sum64 = torch.zeros(1, dtype=torch.float64, device=dev)
+    exchange = None
+    if world > 1 and args.allreduce == "fused":
+        def gather(handle: bytes):
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            return handles
+        exchange = capi.Exchange(world, rank, gather)
+        dist.barrier()
     d2, e2, row2 = d.view(rows, COLS), e.view(rows, COLS), row.view(1, COLS)
     stream = torch.cuda.current_stream().cuda_stream
     lib = capi.lib()
@@ -282,11 +290,15 @@ def run_ours(args) -> None:
         capi.broadcast_binary(d2, row2, capi.ADD, out=e2)
         if events is not None:
             events[2].record()
-        capi.check(lib.fdl_sum_f32(f.data_ptr(), n, sum32.data_ptr(), sum64.data_ptr(), None, 0, stream),
-                   "fdl_sum_f32")
+        if exchange is not None:
+            # sum + exchange of the per-GPU partials over NVLink in ONE kernel
+            exchange.sum(f, sum32, sum64)
+        else:
+            capi.check(lib.fdl_sum_f32(f.data_ptr(), n, sum32.data_ptr(), sum64.data_ptr(), None, 0, stream),
+                       "fdl_sum_f32")
         if events is not None:
             events[3].record()
-        if world > 1:
+        if world > 1 and exchange is None:
             dist.all_reduce(sum64)  # per-GPU partials -> global sum: same stream, no host round trip
 
     def barrier():
@@ -367,7 +379,10 @@ def run_ours(args) -> None:
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "partition": f"leading dimension over {world} GPU(s): {rows} of {args.rows} rows on rank 0",
-                   "l2": "inputs larger than L2 (six distinct tensors stream per step)"},
+                   "l2": "inputs larger than L2 (six distinct tensors stream per step)",
+                   "full_sum_exchange": ("none (1 GPU)" if world == 1 else
+                                         "fused into the sum kernel (peer stores over NVLink)" if exchange is not None
+                                         else "NCCL all-reduce of one double")},
         "clocks": clocks,
         "e2e": {"value": (total_bytes / e2e_sec / 1e9) if e2e_steps else None, "unit": "GB/s",
                 "h2d_bytes_per_step": (2 * args.rows * COLS + world * COLS) * 4,
@@ -396,9 +411,14 @@ def run_ours(args) -> None:
             line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
                                     "sample": f"failed: {exc!r}"}
 
+    torch.cuda.synchronize()
+    capi.take_device_error()  # raises if a bounded device-side wait ran out
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
+        if exchange is not None:
+            exchange.close()
         dist.destroy_process_group()
 
 
@@ -408,6 +428,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: exchange the full-sum partials inside the sum kernel over NVLink peer stores "
+                         "(fused) or with a separate NCCL all-reduce (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--rows", type=int, default=ROWS,

@@ -41,6 +41,11 @@ PROTOTYPES = {
     "fdl_reduce_cols_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "fdl_sum_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     "fdl_sum_f32_static": (_int, [_vp, _i64, _vp, _vp, _vp]),
+    "fdl_exchange_create": (_int, [_int, _int, C.POINTER(C.c_void_p)]),
+    "fdl_exchange_local_handle": (_int, [_vp, C.c_char_p]),
+    "fdl_exchange_connect": (_int, [_vp, C.c_char_p]),
+    "fdl_exchange_destroy": (_int, [_vp]),
+    "fdl_sum_allreduce_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fdl_reduce_rows_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
     "fdl_argmax_rows_f32": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "fdl_reduce_cols_f32": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f64, _vp, _sz, _vp]),
@@ -330,3 +335,33 @@ def host_sweep(x, y, row, z, w) -> float:
     check(lib().fdl_host_sweep_f32(_ptr(x), _ptr(y), _ptr(row), _ptr(z), _ptr(w), rows, cols, C.byref(res)),
           "fdl_host_sweep_f32")
     return res.value
+
+
+# ---- cross-GPU exchange for the fused full sum ----------------------------------------------------
+
+
+class Exchange:
+    """Per-process context of fdl_sum_allreduce_f32.  `gather` is a callable that takes this
+    rank's 64-byte handle and returns the list of all ranks' handles in rank order (for
+    example a wrapper of torch.distributed.all_gather_object)."""
+
+    def __init__(self, world: int, rank: int, gather):
+        self.world, self.rank = world, rank
+        ctx = C.c_void_p()
+        check(lib().fdl_exchange_create(world, rank, C.byref(ctx)), "fdl_exchange_create")
+        self.ctx = ctx
+        buf = C.create_string_buffer(64)
+        check(lib().fdl_exchange_local_handle(self.ctx, buf), "fdl_exchange_local_handle")
+        handles = gather(buf.raw)
+        if len(handles) != world or any(len(h) != 64 for h in handles):
+            raise ValueError("exchange: expected one 64-byte handle per rank")
+        check(lib().fdl_exchange_connect(self.ctx, b"".join(handles)), "fdl_exchange_connect")
+
+    def sum(self, x, out32, out64):
+        check(lib().fdl_sum_allreduce_f32(_ptr(x), x.numel(), _ptr(out32), _ptr(out64), self.ctx, None, 0,
+                                          _stream()), "fdl_sum_allreduce_f32")
+
+    def close(self):
+        if self.ctx:
+            lib().fdl_exchange_destroy(self.ctx)
+            self.ctx = None

@@ -53,6 +53,11 @@ Tuning& tuning();
 // never freed before process exit).  Used when a caller passes scratch == NULL.
 int get_workspace(size_t bytes, void** out);
 
+// One word of host-mapped pinned memory per process in which kernels raise bits when a
+// bounded device-side wait runs out (bit 0: bulk-copy wait, bit 1: cross-GPU exchange wait).
+int error_flag_device_ptr(unsigned int** dev);
+unsigned int read_and_clear_device_error_flag();
+
 // Persistent-grid size: enough blocks to fill every SM `blocks_per_sm` times, but never
 // more than the work needs.
 inline int persistent_grid(const DeviceInfo* info, int blocks_per_sm, int64_t work_blocks) {

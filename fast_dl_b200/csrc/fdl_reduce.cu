@@ -12,6 +12,7 @@
 #include <mutex>
 #include <climits>
 #include <cmath>
+#include <cstring>
 
 #include "fdl_common.cuh"
 
@@ -179,10 +180,36 @@ __device__ __forceinline__ double block_sum_double(double v, double* red) {
 // Scratch layout: [0,256): uint32 arrival counter (zero between launches);
 // [256, ...): one double per cluster.
 
+// Cross-GPU epilogue of the full sum.  Every rank owns a small exchange buffer that its
+// peers can write (double slots[2][kMaxRanks], then unsigned flags[2][kMaxRanks]; mapped
+// into each process with CUDA IPC).  The one CTA that finishes a rank's sum stores the
+// rank's partial into slot [epoch&1][rank] of EVERY rank's buffer over NVLink, fences, and
+// raises flag [epoch&1][rank] there; then it waits -- for a bounded time -- until all flags
+// of its own buffer show the epoch, and adds the slots in rank order.  All ranks add the
+// same numbers in the same order, so all get the same bits, without a separate collective
+// kernel.  Two parities make it safe to start epoch e+1 while a slow peer still reads e.
+constexpr int kMaxRanks = 16;
+constexpr unsigned long long kExchangeWaitNs = 2000000000ull;  // 2 s, then give up
+
+struct SumExchange {
+    int world = 0;  // 0: single GPU, no exchange
+    int rank = 0;
+    unsigned int epoch = 0;
+    double* slots[kMaxRanks] = {};
+    unsigned int* flags[kMaxRanks] = {};
+    unsigned int* error_flag = nullptr;
+};
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 template <int CL, bool VEC>
 __global__ void __launch_bounds__(kSumThreads)
 sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_f64,
-           unsigned int* counter, double* partials) {
+           unsigned int* counter, double* partials, const SumExchange xc) {
     __shared__ double red[kSumThreads / kWarp];
     __shared__ double cluster_slots[kSumMaxCluster];
     __shared__ bool is_last;
@@ -269,7 +296,43 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
     __threadfence();
     double t = 0.0;
     for (unsigned int k = threadIdx.x; k < nclusters; k += kSumThreads) t += __ldcg(partials + k);
-    const double total = block_sum_double<kSumThreads>(t, red);
+    double total = block_sum_double<kSumThreads>(t, red);
+    if (xc.world > 0) {
+        __shared__ double my_total;
+        if (threadIdx.x == 0) my_total = total;
+        __syncthreads();
+        const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks;
+        bool ok = true;
+        if (threadIdx.x < xc.world) {
+            const int peer = threadIdx.x;
+            // Publish to `peer`: value, system-scope fence, then the flag.
+            *reinterpret_cast<volatile double*>(xc.slots[peer] + par + xc.rank) = my_total;
+            __threadfence_system();
+            *reinterpret_cast<volatile unsigned int*>(xc.flags[peer] + par + xc.rank) = xc.epoch;
+            // Wait for `peer`'s flag in this rank's own buffer.
+            volatile unsigned int* mine = xc.flags[xc.rank] + par + peer;
+            const unsigned long long t0 = global_timer_ns();
+            while (*mine != xc.epoch) {
+                if (global_timer_ns() - t0 > kExchangeWaitNs) {
+                    ok = false;
+                    break;
+                }
+            }
+            __threadfence_system();
+        }
+        ok = __syncthreads_and(ok);
+        if (threadIdx.x == 0) {
+            if (ok) {
+                total = 0.0;
+                for (int q = 0; q < xc.world; ++q) {
+                    total += *reinterpret_cast<volatile double*>(xc.slots[xc.rank] + par + q);
+                }
+            } else {
+                total = nan("");
+                atomicOr(xc.error_flag, 2u);
+            }
+        }
+    }
     if (threadIdx.x == 0) {
         if (out_f32 != nullptr) *out_f32 = static_cast<float>(total);
         if (out_f64 != nullptr) *out_f64 = total;
@@ -279,7 +342,7 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
 
 template <int CL, bool VEC>
 int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsigned int* counter,
-               double* partials, cudaStream_t stream) {
+               double* partials, cudaStream_t stream, const SumExchange& xc = SumExchange()) {
     const int64_t nvec = VEC ? n / 4 : 0;
     int64_t tiles = VEC ? ceil_div(nvec, kSumTile) : ceil_div(n, static_cast<int64_t>(kSumTile) * 4);
     if (tiles < 1) tiles = 1;
@@ -288,7 +351,7 @@ int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsig
     if (grid > cap) grid = cap;
     if (CL == 1) {
         sum_kernel<1, VEC><<<static_cast<unsigned int>(grid), kSumThreads, 0, stream>>>(
-            x, n, nvec, out_f32, out_f64, counter, partials);
+            x, n, nvec, out_f32, out_f64, counter, partials, xc);
         return launch_status();
     }
     cudaLaunchConfig_t cfg = {};
@@ -303,7 +366,7 @@ int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsig
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, sum_kernel<CL, VEC>, x, n, nvec, out_f32, out_f64,
-                                       counter, partials);
+                                       counter, partials, xc);
     if (e != cudaSuccess) return static_cast<int>(e);
     return launch_status();
 }
@@ -936,6 +999,123 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
 #undef FDL_LAUNCH_COLS
     if (e != cudaSuccess) return static_cast<int>(e);
     return launch_status();
+}
+
+}  // extern "C"
+
+// ======================================================================================
+// Full sum across the GPUs of one box: the exchange context and the fused entry point
+// ======================================================================================
+
+namespace fdl {
+namespace {
+
+constexpr size_t kExchangeBytes = 4096;
+constexpr size_t kExchangeFlagsOffset = 2 * kMaxRanks * sizeof(double);
+
+struct ExchangeContext {
+    int world = 0;
+    int rank = 0;
+    int device = 0;
+    unsigned int epoch = 0;
+    void* local = nullptr;
+    void* peer[kMaxRanks] = {};
+    bool connected = false;
+};
+
+}  // namespace
+}  // namespace fdl
+
+extern "C" {
+
+int fdl_exchange_create(int world, int rank, void** ctx_out) {
+    if (ctx_out == nullptr || world < 1 || world > kMaxRanks || rank < 0 || rank >= world) {
+        return FDL_ERR_INVALID_ARGUMENT;
+    }
+    auto* ctx = new ExchangeContext();
+    ctx->world = world;
+    ctx->rank = rank;
+    cudaError_t e = cudaGetDevice(&ctx->device);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->local, kExchangeBytes);
+    if (e == cudaSuccess) e = cudaMemset(ctx->local, 0, kExchangeBytes);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return static_cast<int>(e);
+    }
+    ctx->peer[rank] = ctx->local;
+    ctx->connected = world == 1;
+    *ctx_out = ctx;
+    return FDL_OK;
+}
+
+int fdl_exchange_local_handle(void* ctx_in, unsigned char* handle64) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || handle64 == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, ctx->local);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    memcpy(handle64, &h, 64);
+    return FDL_OK;
+}
+
+int fdl_exchange_connect(void* ctx_in, const unsigned char* handles) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || handles == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    for (int p = 0; p < ctx->world; ++p) {
+        if (p == ctx->rank || ctx->peer[p] != nullptr) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + 64 * p, 64);
+        const cudaError_t e = cudaIpcOpenMemHandle(&ctx->peer[p], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    ctx->connected = true;
+    return FDL_OK;
+}
+
+int fdl_exchange_destroy(void* ctx_in) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr) return FDL_OK;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < ctx->world; ++p) {
+        if (p != ctx->rank && ctx->peer[p] != nullptr) cudaIpcCloseMemHandle(ctx->peer[p]);
+    }
+    cudaFree(ctx->local);
+    delete ctx;
+    return FDL_OK;
+}
+
+int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx_in,
+                          void* scratch, size_t scratch_bytes, void* stream) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || !ctx->connected) return FDL_ERR_INVALID_ARGUMENT;
+    if (n < 0 || (out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
+    if (n > 0 && x == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    int status = FDL_OK;
+    const size_t need = fdl_sum_scratch_bytes(n);
+    if (scratch == nullptr) {
+        status = get_workspace(need, &scratch);
+        if (status != FDL_OK) return status;
+    } else if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) {
+        return FDL_ERR_WORKSPACE;
+    }
+    SumExchange xc;
+    xc.world = ctx->world;
+    xc.rank = ctx->rank;
+    ctx->epoch += 1;
+    if (ctx->epoch == 0) ctx->epoch = 1;  // 0 is the buffers' initial state
+    xc.epoch = ctx->epoch;
+    for (int p = 0; p < ctx->world; ++p) {
+        xc.slots[p] = static_cast<double*>(ctx->peer[p]);
+        xc.flags[p] = reinterpret_cast<unsigned int*>(static_cast<char*>(ctx->peer[p]) + kExchangeFlagsOffset);
+    }
+    status = error_flag_device_ptr(&xc.error_flag);
+    if (status != FDL_OK) return status;
+    unsigned int* counter = static_cast<unsigned int*>(scratch);
+    double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
+    cudaStream_t s = as_stream(stream);
+    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s, xc);
+    return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s, xc);
 }
 
 }  // extern "C"

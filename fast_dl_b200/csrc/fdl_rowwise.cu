@@ -316,23 +316,6 @@ __global__ void __launch_bounds__(kPlainThreads) rows_plain_kernel(const RowPara
 
 // ---- host side -------------------------------------------------------------------------------
 
-unsigned int* g_error_flag_host = nullptr;  // mapped pinned memory, one word per process
-
-int error_flag_device_ptr(unsigned int** dev) {
-    if (g_error_flag_host == nullptr) {
-        void* h = nullptr;
-        cudaError_t e = cudaHostAlloc(&h, 256, cudaHostAllocMapped | cudaHostAllocPortable);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        g_error_flag_host = static_cast<unsigned int*>(h);
-        *g_error_flag_host = 0;
-    }
-    void* d = nullptr;
-    cudaError_t e = cudaHostGetDevicePointer(&d, g_error_flag_host, 0);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    *dev = static_cast<unsigned int*>(d);
-    return FDL_OK;
-}
-
 template <class Op, int TPR, int TH, int NV>
 int launch_direct_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream) {
     constexpr int kTeams = TH / TPR;
@@ -412,13 +395,6 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
 
 }  // namespace
 
-unsigned int read_and_clear_device_error_flag() {
-    if (g_error_flag_host == nullptr) return 0;
-    const unsigned int v = *reinterpret_cast<volatile unsigned int*>(g_error_flag_host);
-    *reinterpret_cast<volatile unsigned int*>(g_error_flag_host) = 0;
-    return v;
-}
-
 }  // namespace fdl
 
 using namespace fdl;
@@ -450,10 +426,6 @@ int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta
     p.cols = static_cast<int>(cols);
     p.eps = eps;
     return launch_rows_op<LayerNormOp>(p, as_stream(stream));
-}
-
-int fdl_take_device_error(void) {
-    return read_and_clear_device_error_flag() != 0 ? FDL_ERR_DEVICE_WAIT : FDL_OK;
 }
 
 }  // extern "C"

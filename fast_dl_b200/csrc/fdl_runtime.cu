@@ -23,6 +23,35 @@ Workspace g_workspace[kMaxDevices];
 
 }  // namespace
 
+namespace {
+unsigned int* g_error_flag_host = nullptr;  // mapped pinned memory, one word per process
+}
+
+int error_flag_device_ptr(unsigned int** dev) {
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (g_error_flag_host == nullptr) {
+            void* h = nullptr;
+            cudaError_t e = cudaHostAlloc(&h, 256, cudaHostAllocMapped | cudaHostAllocPortable);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            g_error_flag_host = static_cast<unsigned int*>(h);
+            *g_error_flag_host = 0;
+        }
+    }
+    void* d = nullptr;
+    cudaError_t e = cudaHostGetDevicePointer(&d, g_error_flag_host, 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    *dev = static_cast<unsigned int*>(d);
+    return FDL_OK;
+}
+
+unsigned int read_and_clear_device_error_flag() {
+    if (g_error_flag_host == nullptr) return 0;
+    const unsigned int v = *reinterpret_cast<volatile unsigned int*>(g_error_flag_host);
+    *reinterpret_cast<volatile unsigned int*>(g_error_flag_host) = 0;
+    return v;
+}
+
 Tuning& tuning() {
     static Tuning t;
     return t;
@@ -114,6 +143,10 @@ const char* fdl_error_string(int status) {
     }
     if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
     return "fdl: unknown status";
+}
+
+int fdl_take_device_error(void) {
+    return fdl::read_and_clear_device_error_flag() != 0 ? FDL_ERR_DEVICE_WAIT : FDL_OK;
 }
 
 int fdl_set_tuning(const char* key, int value) {

@@ -189,6 +189,29 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64,
 int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f64,
                        void* stream);
 
+/* ---- full sum across the GPUs of one box (one process per GPU) ------------------------------
+ *
+ * fdl_sum_allreduce_f32 is fdl_sum_f32 plus the exchange of the per-GPU partials, in ONE
+ * kernel: the CTA that finishes a rank's sum stores the partial into a small buffer of every
+ * peer over NVLink (plain peer stores, no multicast), raises a flag there, waits -- at most
+ * two seconds -- for the peers' flags in its own buffer and adds the partials in rank order,
+ * so every rank ends with the same bits and no separate collective kernel is launched.
+ * A wait that runs out writes NaN to the outputs and raises the flag read by
+ * fdl_take_device_error; it never hangs.
+ *
+ * Set-up, once per process: fdl_exchange_create (allocates this rank's 4 KiB buffer on the
+ * current device) -> fdl_exchange_local_handle (64-byte CUDA IPC handle) -> all-gather the
+ * handles with any host mechanism -> fdl_exchange_connect(world * 64 bytes, rank order).
+ * Calls are collective: every rank must call fdl_sum_allreduce_f32 the same number of
+ * times in the same order.  At most 16 ranks.  No counterpart in the reference (which has
+ * no multi-GPU code at all). */
+int fdl_exchange_create(int world, int rank, void** ctx_out);
+int fdl_exchange_local_handle(void* ctx, unsigned char* handle64);
+int fdl_exchange_connect(void* ctx, const unsigned char* handles);
+int fdl_exchange_destroy(void* ctx);
+int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx,
+                          void* scratch, size_t scratch_bytes, void* stream);
+
 /* Row-wise reduction of a row-major [rows, cols] matrix along axis 1:
  * out[r] = op over c of x[r, c]; FDL_REDUCE_MAX ignores NaNs like fmaxf.  No counterpart
  * in the reference (row max / row sum exist only inside its softmax,
