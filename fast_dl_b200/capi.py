@@ -292,6 +292,32 @@ def layernorm_rows(x, gamma=None, beta=None, eps=1e-5, out=None, want_stats=Fals
     return (out, mean, rstd) if want_stats else out
 
 
+def cross_entropy(logits, labels):
+    import torch
+    _require(logits, torch.float32), _require(labels, torch.int64)
+    batch, classes = logits.shape
+    loss = torch.empty(1, dtype=torch.float32, device=logits.device)
+    check(lib().fdl_cross_entropy_f32(_ptr(logits), _ptr(labels), _ptr(loss), batch, classes, _stream()),
+          "fdl_cross_entropy_f32")
+    return loss
+
+
+def transpose(x):
+    import torch
+    _require(x, torch.float32)
+    out = torch.empty_like(x)
+    check(lib().fdl_transpose_f32(_ptr(x), _ptr(out), x.shape[0], _stream()), "fdl_transpose_f32")
+    return out
+
+
+def random_fill(n, normal, p0, p1, seed, device="cuda"):
+    import torch
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    fn = lib().fdl_normal_f32 if normal else lib().fdl_uniform_f32
+    check(fn(_ptr(out), n, p0, p1, seed, _stream()), "fdl_random_fill")
+    return out
+
+
 def take_device_error() -> None:
     check(lib().fdl_take_device_error(), "device-side wait")
 

@@ -317,3 +317,29 @@ void orc_softmax_rows_f64(const float* x, double* y, int64_t rows, int64_t cols)
         for (c = 0; c < cols; ++c) yr[c] /= sum;
     }
 }
+
+/* ---- cross-entropy: per row log(sum exp(x - max)) + max - x[label], mean over the batch
+ * (each term divided by batch before the add); rows with an out-of-range label contribute 0:
+ * src/kernels/cuda/cross_entropy.cu:9-35.  Accumulated in double here. ---- */
+double orc_cross_entropy_f64(const float* logits, const int64_t* labels, int64_t batch, int64_t classes) {
+    double total = 0.0;
+    int64_t r, c;
+    for (r = 0; r < batch; ++r) {
+        const float* x = logits + r * classes;
+        float m;
+        double s = 0.0;
+        if (labels[r] < 0 || labels[r] >= classes) continue;
+        m = x[0];
+        for (c = 1; c < classes; ++c) m = x[c] > m ? x[c] : m;
+        for (c = 0; c < classes; ++c) s += exp((double)x[c] - (double)m);
+        total += (log(s) + (double)m - (double)x[labels[r]]) / (double)batch;
+    }
+    return total;
+}
+
+/* ---- square transpose: src/kernels/cuda/transpose.cu:7-15 ---- */
+void orc_transpose_f32(const float* in, float* out, int64_t n) {
+    int64_t r, c;
+    for (r = 0; r < n; ++r)
+        for (c = 0; c < n; ++c) out[c * n + r] = in[r * n + c];
+}

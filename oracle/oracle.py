@@ -24,6 +24,7 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(str(build_oracle.build()))
         _lib.orc_sum_f64.restype = C.c_double
         _lib.orc_norm2_f64.restype = C.c_double
+        _lib.orc_cross_entropy_f64.restype = C.c_double
     return _lib
 
 
@@ -187,3 +188,17 @@ def ulp_distance(a, b):
     a = np.where(a < 0, np.int64(-(2 ** 31)) - a, a)
     b = np.where(b < 0, np.int64(-(2 ** 31)) - b, b)
     return np.abs(a - b)
+
+
+def cross_entropy(logits, labels) -> float:
+    logits, pl = _f(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    batch, classes = logits.shape
+    return float(lib().orc_cross_entropy_f64(pl, labels.ctypes.data_as(_ip), C.c_int64(batch), C.c_int64(classes)))
+
+
+def transpose(x):
+    x, px = _f(x)
+    out = np.empty_like(x)
+    lib().orc_transpose_f32(px, out.ctypes.data_as(_fp), C.c_int64(x.shape[0]))
+    return out

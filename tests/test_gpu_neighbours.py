@@ -1,0 +1,47 @@
+"""GPU parity of the path's neighbours: cross-entropy, transpose, random fill."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.helpers import assert_bit_exact, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("batch,classes", [(1, 1), (3, 5), (64, 1000), (4096, 37), (257, 4096)])
+def test_cross_entropy(fdl, cuda, batch, classes):
+    rng = np.random.default_rng(42)
+    logits = rng.normal(0, 3, (batch, classes)).astype(np.float32)
+    labels = rng.integers(0, classes, batch).astype(np.int64)
+    if batch > 2:
+        labels[1] = -1          # invalid labels are skipped, as in the reference kernel
+        labels[2] = classes
+    got = to_np(fdl.cross_entropy(cuda.from_numpy(logits).cuda(), cuda.from_numpy(labels).cuda()))[0]
+    want = orc.cross_entropy(logits, labels)
+    assert abs(got - want) <= 1e-5 * max(1.0, abs(want))   # the reference test allows 1e-4
+    again = to_np(fdl.cross_entropy(cuda.from_numpy(logits).cuda(), cuda.from_numpy(labels).cuda()))[0]
+    assert got == again  # deterministic: no float atomics
+
+
+@pytest.mark.parametrize("n", [1, 31, 32, 33, 100, 1024, 4096])
+def test_transpose_bit_exact(fdl, cuda, n):
+    rng = np.random.default_rng(42)
+    x = rng.normal(size=(n, n)).astype(np.float32)
+    got = to_np(fdl.transpose(cuda.from_numpy(x).cuda()))
+    assert_bit_exact(got, orc.transpose(x), f"transpose {n}")
+    assert_bit_exact(got, x.T, "vs numpy")
+
+
+def test_random_fill_properties(fdl, cuda):
+    n = (1 << 20) + 3
+    u1 = to_np(fdl.random_fill(n, False, -2.0, 3.0, 1234))
+    u2 = to_np(fdl.random_fill(n, False, -2.0, 3.0, 1234))
+    u3 = to_np(fdl.random_fill(n, False, -2.0, 3.0, 1235))
+    assert np.array_equal(u1, u2) and not np.array_equal(u1, u3)     # what the reference's tests pin
+    assert u1.min() > -2.0 and u1.max() <= 3.0
+    assert abs(u1.mean() - 0.5) < 0.01 and abs(u1.std() - 5 / np.sqrt(12)) < 0.01
+    # a prefix of a longer fill equals the shorter fill: values depend on (seed, index) only
+    assert np.array_equal(to_np(fdl.random_fill(1000, False, -2.0, 3.0, 1234)), u1[:1000])
+    g = to_np(fdl.random_fill(n, True, 1.0, 2.0, 99))
+    assert np.isfinite(g).all() and abs(g.mean() - 1.0) < 0.01 and abs(g.std() - 2.0) < 0.01
+    assert np.array_equal(g, to_np(fdl.random_fill(n, True, 1.0, 2.0, 99)))
