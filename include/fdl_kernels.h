@@ -164,7 +164,9 @@ size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols);
  * before the final rounding to float (what a multi-GPU caller all-reduces).
  * Deterministic: same input, same launch -> same bits.  `scratch` may be NULL, in
  * which case the library uses a per-device workspace it allocates on first use and
- * keeps; otherwise it must hold fdl_sum_scratch_bytes(n).  No counterpart in the
+ * keeps; otherwise it must hold fdl_sum_scratch_bytes(n), be 256-byte aligned, and have had
+ * its first 256 bytes zeroed once (the kernel leaves them zero).  Calls that may overlap on
+ * the GPU (different streams) must not share scratch: pass each its own.  No counterpart in the
  * reference, whose reduction stops at one partial per 1024 elements
  * (src/kernels/cuda/reduction.cu:34-57). */
 int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64,
