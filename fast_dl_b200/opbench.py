@@ -1,14 +1,15 @@
 """Per-operation bandwidth table for the five workload configurations.
 
-    python -m fast_dl_b200.opbench [--configs c1,c2,c3,c4,c5] [--iters 20] [--reference] [--json out.json]
+    python -m fast_dl_b200.opbench [--configs c1,c2,c3,c4,c5] [--iters 20] [--json out.json]
 
 For every op of every configuration it reports the median launch time (CUDA events around
 each launch; between launches the L2 is flushed by READING a 512 MiB buffer, which leaves
 clean lines behind -- flushing by writing would leave ~100 MB of dirty lines whose
 write-back is then billed to the kernel under test), the algorithmic
 GB/s (compulsory bytes only) and that as a fraction of the measured HBM copy bandwidth.
-With --reference the reference's own CUDA kernels (compiled in place into oracle/_ref by
-oracle/build_ref.py, test infrastructure) are timed on the same buffers as the speed bar.
+A caller may hand main() an object with the reference's own kernel launchers; they are then
+timed on the same buffers as the speed bar (tests/opbench_reference.py does that with the
+reference's kernels recompiled for sm_100a).  This module itself knows only the product.
 """
 from __future__ import annotations
 
@@ -30,14 +31,13 @@ def peak_gbs() -> float:
     return 6650.0
 
 
-def main() -> None:
+def main(ref=None) -> None:
     import torch
     from fast_dl_b200 import capi
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c2,c3,c4,c5")
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--reference", action="store_true")
     ap.add_argument("--json", default=None)
     ap.add_argument("--tune", action="append", default=[], help="key=value passed to fdl_set_tuning")
     args = ap.parse_args()
@@ -52,11 +52,6 @@ def main() -> None:
     peak = peak_gbs()
     flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
     gen = torch.Generator(device=dev).manual_seed(42)
-    ref = None
-    if args.reference:
-        from oracle import ref as _ref
-        if _ref.available():
-            ref = _ref
 
     def uniform(shape, lo=-1.0, hi=1.0):
         return torch.empty(shape, dtype=torch.float32, device=dev).uniform_(lo, hi, generator=gen)
