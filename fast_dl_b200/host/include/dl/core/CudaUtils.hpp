@@ -17,4 +17,7 @@ void check_fdl(int status, const char* action);
 /// library's (they may be separate runtime instances when linked statically).
 void set_device(int device_index);
 
+/// Number of visible CUDA devices (0 when there is no driver).
+int device_count();
+
 }  // namespace dl::cuda

@@ -76,5 +76,14 @@ void set_device(int device_index) {
     check_fdl(fdl_set_device(device_index), "cudaSetDevice failed");
 }
 
+int device_count() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
 }  // namespace cuda
 }  // namespace dl

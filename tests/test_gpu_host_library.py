@@ -32,8 +32,9 @@ def test_reference_program_passes_against_this_library(cuda, name):
     assert "not passed" not in proc.stdout and "passed" in proc.stdout, proc.stdout
 
 
-def test_host_library_additions(cuda):
-    exe = ROOT / "fast_dl_b200" / "lib" / "host_ops_test"
+@pytest.mark.parametrize("program", ["host_ops_test", "sharded_test"])
+def test_host_library_additions(cuda, program):
+    exe = ROOT / "fast_dl_b200" / "lib" / program
     assert exe.exists(), "run python -m fast_dl_b200.build core"
     proc = run(exe)
     assert proc.returncode == 0 and "not passed" not in proc.stdout, proc.stdout + proc.stderr
