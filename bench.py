@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Bench of the fast_dl tensor hot path on B200: effective GB/s and fraction of the HBM roofline.
 
-Workload (BASELINE.json config 5): the large-tensor sweep over 268,435,456 fp32 elements,
+Workload: the large-tensor sweep over 268,435,456 fp32 elements,
 uniform [-1, 1], viewed as [16384, 16384].  One "step" is
     z = x + y                 binary add                       12 B/element
     w = x + row[1, 16384]     broadcast add against a row       8 B/element (+ the row)

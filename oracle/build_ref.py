@@ -3,7 +3,8 @@
     python -m oracle.build_ref
 
 Nothing from the reference is copied into this repository: the reference's sources are
-compiled where they lie (REFERENCE_ROOT, default /root/reference) and only build outputs
+compiled where they lie (environment variable REFERENCE_ROOT; by default the directory
+`reference` beside this repository) and only build outputs
 land in oracle/_ref/, which is git-ignored but travels with the working tree to a GPU
 box.  The reference's CMake build is NOT run; these are direct gcc/nvcc invocations on the
 few files the path needs.  When the reference tree is absent this is a no-op and the
@@ -31,7 +32,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("REFERENCE_ROOT", str(ROOT.parent / "reference")))
 OUT = HERE / "_ref"
 SHIMS = HERE / "ref_shims"
 

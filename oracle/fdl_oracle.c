@@ -13,7 +13,7 @@
  * separately, and gcc would otherwise be free to fuse them on FMA hardware.
  *
  * Pinning status
- *   PINNED by the reference's own vectors (tests/golden/reference_vectors.json, taken
+ *   PINNED by the reference's own vectors (tests/golden/reference_vectors.npz, taken
  *   from tests/tensor/elementwise_tensor_test.cpp:30-63, tests/nn/relu_module_test.cpp:22-29,
  *   tests/tensor/activation_tensor_test.cpp:71-74, tests/tensor/softmax_tensor_test.cpp:43-46,
  *   tests/tensor/layernorm_tensor_test.cpp:50-53) and by oracle/_ref (the reference's CPU

@@ -1,6 +1,7 @@
 """Generates tests/golden/reference_vectors.npz from the reference itself.
 
-Run in a container that has the reference tree (REFERENCE_ROOT, default /root/reference):
+Run where the reference tree is available (environment variable REFERENCE_ROOT; by default the
+directory `reference` beside this repository):
 
     python tests/golden/make_golden.py
 
@@ -25,7 +26,7 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("REFERENCE_ROOT", str(ROOT.parent / "reference")))
 
 from oracle import build_ref, ref  # noqa: E402
 
