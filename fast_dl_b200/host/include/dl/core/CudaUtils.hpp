@@ -20,4 +20,7 @@ void set_device(int device_index);
 /// Number of visible CUDA devices (0 when there is no driver).
 int device_count();
 
+/// Blocks until all work enqueued on the current device has finished.
+void synchronize();
+
 }  // namespace dl::cuda

@@ -76,6 +76,8 @@ void set_device(int device_index) {
     check_fdl(fdl_set_device(device_index), "cudaSetDevice failed");
 }
 
+void synchronize() { check(cudaDeviceSynchronize(), "cudaDeviceSynchronize failed"); }
+
 int device_count() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess) {
