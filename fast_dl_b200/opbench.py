@@ -170,5 +170,147 @@ def main(ref=None) -> None:
         Path(args.json).write_text(json.dumps({"peak_gbs": peak, "results": results}, indent=1))
 
 
+def main_sharded() -> None:
+    """Per-op table with every tensor row-sharded over the ranks of a torch.distributed job.
+
+        python -m torch.distributed.run --nproc-per-node N -m fast_dl_b200.opbench --sharded [--json out.json]
+
+    Configurations C2-C5, total sizes fixed (strong scaling).  Every rank times its shard
+    (CUDA events per launch, read-flushed L2, median of --iters launches); the slowest rank
+    defines the time.  Aggregate GB/s = whole-tensor algorithmic bytes / that time; the
+    per-GPU fraction divides by N x the measured copy bandwidth.  Ops with an exchange: full
+    sum (partials exchanged inside the kernel over NVLink), mean along axis 0 (NCCL
+    all-reduce of [cols] floats, included in the time).
+    """
+    import os
+
+    import torch
+    import torch.distributed as dist
+    from fast_dl_b200 import capi
+    from fast_dl_b200.sharding import shard_rows
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sharded", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    capi.lib()
+    capi.use_device(local)
+    dev = torch.device("cuda", local)
+    exchange = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+        def gather(handle):
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            return handles
+        exchange = capi.Exchange(world, rank, gather)
+        dist.barrier()
+    peak = peak_gbs()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(42 + rank)
+    results = []
+
+    def rnd(shape, kind="u", a=-1.0, b=1.0):
+        t = torch.empty(shape, dtype=torch.float32, device=dev)
+        return t.uniform_(a, b, generator=gen) if kind == "u" else t.normal_(a, b, generator=gen)
+
+    def record(config, op, total_bytes, fn):
+        times = []
+        for i in range(args.iters + 3):
+            if world > 1:
+                dist.barrier()  # ranks start each launch together, as a sharded op would
+            # The flush (~80 us) also lets the host enqueue the timed launch before the GPU
+            # gets to it, so no host launch latency is measured.
+            capi.full_sum(flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+        gbs = total_bytes / ms / 1e6
+        results.append({"config": config, "op": op, "n_gpus": world, "bytes": total_bytes, "ms": ms, "GBps": gbs,
+                        "frac_per_gpu": gbs / (world * peak)})
+        if rank == 0:
+            print(f"{config:3s} {op:40s} {ms * 1e3:9.1f} us {gbs:9.1f} GB/s  {100 * gbs / (world * peak):5.1f}% per GPU",
+                  flush=True)
+
+    s32 = torch.zeros(1, dtype=torch.float32, device=dev)
+    s64 = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    def total_sum(x):
+        if exchange is not None:
+            exchange.sum(x.reshape(-1), s32, s64)
+        else:
+            capi.full_sum(x.reshape(-1))
+
+    # C2
+    R = C = 4096
+    r = shard_rows(R, world, rank).count
+    A, bias, scale = rnd((r, C), "n", 0.0, 1.0), rnd((1, C), "n", 0.0, 1.0), rnd((r, 1), "u", 0.5, 2.0)
+    out = torch.empty_like(A)
+    record("c2", "A + b[1,4096]", 8 * R * C + 4 * C * world, lambda: capi.broadcast_binary(A, bias, capi.ADD, out=out))
+    record("c2", "A * s[4096,1]", 8 * R * C + 4 * R, lambda: capi.broadcast_binary(A, scale, capi.MUL, out=out))
+    del A, out
+    # C3
+    R = C = 8192
+    r = shard_rows(R, world, rank).count
+    X = rnd((r, C), "n", 0.0, 1.0)
+    record("c3", "sum axis 1", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_SUM))
+    record("c3", "max axis 1", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_MAX))
+    record("c3", "argmax axis 1 (int64)", 4 * R * C + 8 * R, lambda: capi.argmax_rows(X))
+
+    def mean0():
+        m = capi.reduce_cols(X, capi.REDUCE_MEAN, mean_divisor=R)
+        if world > 1:
+            dist.all_reduce(m)
+    record("c3", "mean axis 0 (+ all-reduce of [8192])", 4 * R * C + 4 * C * world, mean0)
+    record("c3", "full sum (+ exchange)", 4 * R * C + 4, lambda: total_sum(X))
+    del X
+    # C4
+    R, C = 65536, 1024
+    r = shard_rows(R, world, rank).count
+    L = rnd((r, C), "n", 0.0, 3.0)
+    g, be = rnd(C, "u", 0.9, 1.1), rnd(C, "u", -0.1, 0.1)
+    out = torch.empty_like(L)
+    record("c4", "row softmax", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
+    record("c4", "layernorm + gamma, beta", 8 * R * C + 8 * C * world, lambda: capi.layernorm_rows(L, g, be, out=out))
+    record("c4", "activation gelu", 8 * R * C, lambda: capi.unary(L, capi.GELU, out=out))
+    del L, out
+    # C5
+    R, C = 16384, 16384
+    r = shard_rows(R, world, rank).count
+    x, y, row = rnd(r * C), rnd(r * C), rnd((1, C))
+    out = torch.empty_like(x)
+    n = R * C
+    record("c5", "binary add", 12 * n, lambda: capi.binary(x, y, capi.ADD, out=out))
+    record("c5", "broadcast add [16384,16384]+[1,16384]", 8 * n + 4 * C * world,
+           lambda: capi.broadcast_binary(x.view(r, C), row, capi.ADD, out=out.view(r, C)))
+    record("c5", "full sum (+ exchange)", 4 * n + 4, lambda: total_sum(x))
+
+    torch.cuda.synchronize()
+    capi.take_device_error()
+    if rank == 0 and args.json:
+        Path(args.json).write_text(json.dumps({"peak_gbs": peak, "n_gpus": world, "results": results}, indent=1))
+    if world > 1:
+        dist.barrier()
+        exchange.close()
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
-    main()
+    if "--sharded" in sys.argv:
+        main_sharded()
+    else:
+        main()
