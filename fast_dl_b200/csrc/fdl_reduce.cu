@@ -181,13 +181,16 @@ __device__ __forceinline__ double block_sum_double(double v, double* red) {
 // [256, ...): one double per cluster.
 
 // Cross-GPU epilogue of the full sum.  Every rank owns a small exchange buffer that its
-// peers can write (double slots[2][kMaxRanks], then unsigned flags[2][kMaxRanks]; mapped
-// into each process with CUDA IPC).  The one CTA that finishes a rank's sum stores the
-// rank's partial into slot [epoch&1][rank] of EVERY rank's buffer over NVLink, fences, and
-// raises flag [epoch&1][rank] there; then it waits -- for a bounded time -- until all flags
-// of its own buffer show the epoch, and adds the slots in rank order.  All ranks add the
-// same numbers in the same order, so all get the same bits, without a separate collective
-// kernel.  Two parities make it safe to start epoch e+1 while a slow peer still reads e.
+// peers can write (uint64 words[2][kMaxRanks][2]; mapped into each process with CUDA IPC).
+// The one CTA that finishes a rank's sum sends the rank's partial (a double) to EVERY
+// rank's buffer over NVLink as two self-validating 8-byte words, {high half, epoch} and
+// {low half, epoch}, into entry [epoch&1][rank]: an 8-byte store is indivisible, so a reader
+// that sees the epoch in both words has the whole value, and no fence or separate flag
+// write sits between data and notification.  The CTA then waits -- for a bounded time --
+// until all entries of its own buffer show the epoch, and adds the values in rank order.
+// All ranks add the same numbers in the same order, so all get the same bits, without a
+// separate collective kernel.  Two parities make it safe to start epoch e+1 while a slow
+// peer still reads e.
 constexpr int kMaxRanks = 16;
 constexpr unsigned long long kExchangeWaitNs = 2000000000ull;  // 2 s, then give up
 
@@ -195,8 +198,7 @@ struct SumExchange {
     int world = 0;  // 0: single GPU, no exchange
     int rank = 0;
     unsigned int epoch = 0;
-    double* slots[kMaxRanks] = {};
-    unsigned int* flags[kMaxRanks] = {};
+    unsigned long long* words[kMaxRanks] = {};  // each rank's buffer
     unsigned int* error_flag = nullptr;
 };
 
@@ -301,32 +303,39 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
         __shared__ double my_total;
         if (threadIdx.x == 0) my_total = total;
         __syncthreads();
-        const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks;
+        const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks * 2;
+        const unsigned long long tag = xc.epoch;
         bool ok = true;
+        double from_peer = 0.0;
         if (threadIdx.x < xc.world) {
             const int peer = threadIdx.x;
-            // Publish to `peer`: value, system-scope fence, then the flag.
-            *reinterpret_cast<volatile double*>(xc.slots[peer] + par + xc.rank) = my_total;
-            __threadfence_system();
-            *reinterpret_cast<volatile unsigned int*>(xc.flags[peer] + par + xc.rank) = xc.epoch;
-            // Wait for `peer`'s flag in this rank's own buffer.
-            volatile unsigned int* mine = xc.flags[xc.rank] + par + peer;
+            // Send to `peer`: two indivisible 8-byte stores, each carrying the epoch.
+            const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(my_total));
+            volatile unsigned long long* dst = xc.words[peer] + par + 2 * xc.rank;
+            dst[0] = ((bits >> 32) << 32) | tag;
+            dst[1] = ((bits & 0xffffffffull) << 32) | tag;
+            // Receive `peer`'s value from this rank's own buffer.
+            volatile unsigned long long* src = xc.words[xc.rank] + par + 2 * peer;
             const unsigned long long t0 = global_timer_ns();
-            while (*mine != xc.epoch) {
-                if (global_timer_ns() - t0 > kExchangeWaitNs) {
+            unsigned long long w0 = src[0], w1 = src[1];
+            unsigned int polls = 0;
+            while ((w0 & 0xffffffffull) != tag || (w1 & 0xffffffffull) != tag) {
+                if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
                     ok = false;
                     break;
                 }
+                w0 = src[0];
+                w1 = src[1];
             }
-            __threadfence_system();
+            from_peer = __longlong_as_double(static_cast<long long>(((w0 >> 32) << 32) | (w1 >> 32)));
         }
+        __shared__ double gathered[kMaxRanks];
+        if (threadIdx.x < xc.world) gathered[threadIdx.x] = from_peer;
         ok = __syncthreads_and(ok);
         if (threadIdx.x == 0) {
             if (ok) {
                 total = 0.0;
-                for (int q = 0; q < xc.world; ++q) {
-                    total += *reinterpret_cast<volatile double*>(xc.slots[xc.rank] + par + q);
-                }
+                for (int q = 0; q < xc.world; ++q) total += gathered[q];  // rank order
             } else {
                 total = nan("");
                 atomicOr(xc.error_flag, 2u);
@@ -1011,7 +1020,6 @@ namespace fdl {
 namespace {
 
 constexpr size_t kExchangeBytes = 4096;
-constexpr size_t kExchangeFlagsOffset = 2 * kMaxRanks * sizeof(double);
 
 struct ExchangeContext {
     int world = 0;
@@ -1105,10 +1113,7 @@ int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out
     ctx->epoch += 1;
     if (ctx->epoch == 0) ctx->epoch = 1;  // 0 is the buffers' initial state
     xc.epoch = ctx->epoch;
-    for (int p = 0; p < ctx->world; ++p) {
-        xc.slots[p] = static_cast<double*>(ctx->peer[p]);
-        xc.flags[p] = reinterpret_cast<unsigned int*>(static_cast<char*>(ctx->peer[p]) + kExchangeFlagsOffset);
-    }
+    for (int p = 0; p < ctx->world; ++p) xc.words[p] = static_cast<unsigned long long*>(ctx->peer[p]);
     status = error_flag_device_ptr(&xc.error_flag);
     if (status != FDL_OK) return status;
     unsigned int* counter = static_cast<unsigned int*>(scratch);

@@ -195,8 +195,8 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
  *
  * fdl_sum_allreduce_f32 is fdl_sum_f32 plus the exchange of the per-GPU partials, in ONE
  * kernel: the CTA that finishes a rank's sum stores the partial into a small buffer of every
- * peer over NVLink (plain peer stores, no multicast), raises a flag there, waits -- at most
- * two seconds -- for the peers' flags in its own buffer and adds the partials in rank order,
+ * peer over NVLink (plain 8-byte peer stores that carry an epoch tag, no multicast), waits --
+ * at most two seconds -- for the peers' tagged values in its own buffer and adds them in rank order,
  * so every rank ends with the same bits and no separate collective kernel is launched.
  * A wait that runs out writes NaN to the outputs and raises the flag read by
  * fdl_take_device_error; it never hangs.
