@@ -148,7 +148,11 @@ constexpr int kSumUnroll = 8;                                  // 128-bit loads 
 constexpr int kSumTile = kSumThreads * kSumUnroll;             // float4 per tile (32 KiB)
 constexpr int kSumMaxCluster = 8;
 constexpr int kSumMaxPartials = 8192;                          // doubles in scratch
-constexpr int kCounterBytes = 256;
+// Scratch layout shared by the full sum and the column reductions: a fixed 64 KiB region of
+// arrival counters that every kernel leaves zeroed, then the partials.  The region has the
+// same size for every problem so that one scratch buffer can serve calls of any shape.
+constexpr int kCounterBytes = 65536;
+constexpr int kStaticCounterBytes = 256;  // the static-scratch entry point has its own array
 
 // Block-wide sum in double; result valid in thread 0.  `red` holds one slot per warp.
 template <int THREADS>
@@ -177,8 +181,8 @@ __device__ __forceinline__ double block_sum_double(double v, double* red) {
 // one double per cluster to scratch.  The last cluster to arrive (ticket counter) folds
 // the per-cluster partials in index order, so the result does not depend on scheduling.
 //
-// Scratch layout: [0,256): uint32 arrival counter (zero between launches);
-// [256, ...): one double per cluster.
+// Scratch layout: [0, 64 KiB): arrival counters (this kernel uses the first; zero between
+// launches); then one double per cluster.
 
 // Cross-GPU epilogue of the full sum.  Every rank owns a small exchange buffer that its
 // peers can write (uint64 words[2][kMaxRanks][2]; mapped into each process with CUDA IPC).
@@ -206,6 +210,47 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+// Cross-GPU epilogue of the column reductions: the same protocol, one 8-byte word
+// {float bits, epoch} per column.  A rank's buffer holds words[2][world][kExchangeMaxCols].
+constexpr int kExchangeMaxCols = 65536;
+
+struct ColsExchange {
+    int world = 0;  // 0: single GPU, no exchange
+    int rank = 0;
+    unsigned int epoch = 0;
+    unsigned long long* words[kMaxRanks] = {};  // each rank's vector region
+    unsigned int* error_flag = nullptr;
+};
+
+// Sends this rank's finished value of column `col` to every rank and folds the values of
+// all ranks in rank order (each rank computes the same result).  Bounded wait.
+template <class R>
+__device__ __forceinline__ float exchange_column(const ColsExchange& xc, int64_t col, float value) {
+    const unsigned long long tag = xc.epoch;
+    const int64_t par = static_cast<int64_t>(xc.epoch & 1u) * xc.world * kExchangeMaxCols;
+    const unsigned long long word = (static_cast<unsigned long long>(__float_as_uint(value)) << 32) | tag;
+    for (int p = 0; p < xc.world; ++p) {
+        volatile unsigned long long* dst = xc.words[p] + par + static_cast<int64_t>(xc.rank) * kExchangeMaxCols + col;
+        *dst = word;
+    }
+    float acc = R::identity();
+    const unsigned long long t0 = global_timer_ns();
+    for (int q = 0; q < xc.world; ++q) {
+        volatile unsigned long long* src = xc.words[xc.rank] + par + static_cast<int64_t>(q) * kExchangeMaxCols + col;
+        unsigned long long w = *src;
+        unsigned int polls = 0;
+        while ((w & 0xffffffffull) != tag) {
+            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
+                atomicOr(xc.error_flag, 2u);
+                return nanf("");
+            }
+            w = *src;
+        }
+        acc = R::combine(acc, __uint_as_float(static_cast<unsigned int>(w >> 32)));
+    }
+    return acc;
 }
 
 template <int CL, bool VEC>
@@ -586,8 +631,8 @@ int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out
 // folded in shared memory; chunk partials go to scratch and the last chunk to arrive for
 // a column block folds them in chunk order.
 //
-// Scratch layout: [0, 4*ncounters) counters padded to 256 B, then
-// float partials[chunks][batch][cols].
+// Scratch layout: [0, 64 KiB) one arrival counter per column block (zero between launches),
+// then float partials[groups][batch][cols].
 
 constexpr int kColThreads = 256;
 
@@ -603,7 +648,8 @@ struct ColMax {
 template <class R, int W, int CL>
 __global__ void __launch_bounds__(kColThreads)
 reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float* partials,
-                   unsigned int* counters, int tx, int rows_per_chunk, float scale) {
+                   unsigned int* counters, int tx, int rows_per_chunk, float scale,
+                   const ColsExchange xc) {
     extern __shared__ float tile[];  // [TY][TX*W]
     __shared__ bool is_last;
     const int ty_count = kColThreads / tx;
@@ -701,7 +747,14 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     float* dst = groups == 1 ? out + b * cols
                              : partials + (static_cast<int64_t>(group) * gridDim.z + b) * cols;
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
-        if (col0 + c < cols) dst[col0 + c] = groups == 1 ? tile[c] * scale : tile[c];
+        if (col0 + c >= cols) continue;
+        if (groups != 1) {
+            dst[col0 + c] = tile[c];
+        } else if (xc.world == 0) {
+            dst[col0 + c] = tile[c] * scale;
+        } else {
+            dst[col0 + c] = exchange_column<R>(xc, col0 + c, tile[c] * scale);
+        }
     }
     if (groups == 1) return;
 
@@ -735,7 +788,9 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
             for (int j = 0; j < 8; ++j) s = R::combine(s, v[j]);
         }
         for (; k < groups; ++k) s = R::combine(s, __ldcg(src + k * stride));
-        out[b * cols + col0 + c] = s * scale;
+        s *= scale;
+        if (xc.world > 0) s = exchange_column<R>(xc, col0 + c, s);
+        out[b * cols + col0 + c] = s;
     }
 }
 
@@ -780,7 +835,8 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     }
     const int groups = g->chunks / g->cluster;
     const size_t ncounters = static_cast<size_t>(g->col_blocks) * batch;
-    g->counter_bytes = ((ncounters * sizeof(unsigned int) + 255) / 256) * 256;
+    if (ncounters * sizeof(unsigned int) > static_cast<size_t>(kCounterBytes)) return FDL_ERR_UNSUPPORTED;
+    g->counter_bytes = kCounterBytes;
     g->scratch_bytes =
         groups == 1
             ? 0
@@ -878,7 +934,7 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void
 // writes more than kSumMaxPartials partials whatever n is (CTAs loop over tiles beyond
 // that).  The element count is nevertheless capped at a stated maximum.
 constexpr int64_t kStaticSumMaxElems = int64_t{1} << 30;
-static __device__ __align__(256) unsigned char g_static_sum_scratch[kCounterBytes + kSumMaxPartials * sizeof(double)];
+static __device__ __align__(256) unsigned char g_static_sum_scratch[kStaticCounterBytes + kSumMaxPartials * sizeof(double)];
 
 static std::mutex g_static_mutex;
 static void* g_static_sum_ptr[64] = {};
@@ -905,10 +961,10 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
     }
     cudaStream_t s = as_stream(stream);
     // The array keeps whatever the previous call left: the arrival counter must start at 0.
-    e = cudaMemsetAsync(scratch, 0, kCounterBytes, s);
+    e = cudaMemsetAsync(scratch, 0, kStaticCounterBytes, s);
     if (e != cudaSuccess) return static_cast<int>(e);
     unsigned int* counter = static_cast<unsigned int*>(scratch);
-    double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
+    double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kStaticCounterBytes);
     // Fixed launch shape (clusters of 4): at most kSumMaxPartials partials are written.
     if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s);
     return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s);
@@ -944,9 +1000,9 @@ size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols) 
     return gv.scratch_bytes > gs.scratch_bytes ? gv.scratch_bytes : gs.scratch_bytes;
 }
 
-int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out,
-                        int op, double mean_divisor, void* scratch, size_t scratch_bytes,
-                        void* stream) {
+static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out,
+                            int op, double mean_divisor, void* scratch, size_t scratch_bytes,
+                            void* stream, const ColsExchange& xc) {
     if (batch < 0 || rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
     if (batch == 0 || cols == 0) return FDL_OK;
     if (x == nullptr || out == nullptr || rows == 0) return FDL_ERR_INVALID_ARGUMENT;
@@ -961,7 +1017,8 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
 
     const bool vec = aligned16(x) && cols % 4 == 0;
     ColsGeometry g;
-    cols_geometry(info->sm_count, batch, rows, cols, vec, &g);
+    status = cols_geometry(info->sm_count, batch, rows, cols, vec, &g);
+    if (status != FDL_OK) return status;
     float* partials = nullptr;
     unsigned int* counters = nullptr;
     if (g.chunks / g.cluster > 1) {
@@ -992,7 +1049,7 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
     cudaError_t e;
 #define FDL_LAUNCH_COLS(R, W, CL)                                                              \
     e = cudaLaunchKernelEx(&cfg, reduce_cols_kernel<R, W, CL>, x, rows, cols, out, partials,  \
-                           counters, g.tx, g.rows_per_chunk, scale)
+                           counters, g.tx, g.rows_per_chunk, scale, xc)
 #define FDL_LAUNCH_COLS_CL(CL)                                                                  \
     do {                                                                                        \
         if (is_max) { if (vec) FDL_LAUNCH_COLS(ColMax, 4, CL); else FDL_LAUNCH_COLS(ColMax, 1, CL); } \
@@ -1010,6 +1067,13 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
     return launch_status();
 }
 
+int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out,
+                        int op, double mean_divisor, void* scratch, size_t scratch_bytes,
+                        void* stream) {
+    return reduce_cols_impl(x, batch, rows, cols, out, op, mean_divisor, scratch, scratch_bytes, stream,
+                            ColsExchange());
+}
+
 }  // extern "C"
 
 // ======================================================================================
@@ -1019,13 +1083,18 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
 namespace fdl {
 namespace {
 
-constexpr size_t kExchangeBytes = 4096;
+constexpr size_t kExchangeSumBytes = 4096;  // the full sum's words, then the column-vector region
+
+size_t exchange_bytes(int world) {
+    return kExchangeSumBytes + 2 * static_cast<size_t>(world) * kExchangeMaxCols * sizeof(unsigned long long);
+}
 
 struct ExchangeContext {
     int world = 0;
     int rank = 0;
     int device = 0;
-    unsigned int epoch = 0;
+    unsigned int epoch = 0;      // full-sum exchanges so far
+    unsigned int epoch_cols = 0; // column-vector exchanges so far
     void* local = nullptr;
     void* peer[kMaxRanks] = {};
     bool connected = false;
@@ -1044,8 +1113,8 @@ int fdl_exchange_create(int world, int rank, void** ctx_out) {
     ctx->world = world;
     ctx->rank = rank;
     cudaError_t e = cudaGetDevice(&ctx->device);
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->local, kExchangeBytes);
-    if (e == cudaSuccess) e = cudaMemset(ctx->local, 0, kExchangeBytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->local, exchange_bytes(world));
+    if (e == cudaSuccess) e = cudaMemset(ctx->local, 0, exchange_bytes(world));
     if (e != cudaSuccess) {
         delete ctx;
         return static_cast<int>(e);
@@ -1121,6 +1190,27 @@ int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out
     cudaStream_t s = as_stream(stream);
     if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s, xc);
     return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s, xc);
+}
+
+int fdl_reduce_cols_allreduce_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,
+                                  double mean_divisor, void* ctx_in, void* scratch, size_t scratch_bytes,
+                                  void* stream) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || !ctx->connected) return FDL_ERR_INVALID_ARGUMENT;
+    if (cols > kExchangeMaxCols) return FDL_ERR_UNSUPPORTED;
+    if (rows <= 0 || cols <= 0) return FDL_ERR_INVALID_ARGUMENT;  // collective: every rank must launch
+    ColsExchange xc;
+    xc.world = ctx->world;
+    xc.rank = ctx->rank;
+    ctx->epoch_cols += 1;
+    if (ctx->epoch_cols == 0) ctx->epoch_cols = 1;
+    xc.epoch = ctx->epoch_cols;
+    for (int p = 0; p < ctx->world; ++p) {
+        xc.words[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx->peer[p]) + kExchangeSumBytes);
+    }
+    const int status = error_flag_device_ptr(&xc.error_flag);
+    if (status != FDL_OK) return status;
+    return reduce_cols_impl(x, 1, rows, cols, out, op, mean_divisor, scratch, scratch_bytes, stream, xc);
 }
 
 }  // extern "C"

@@ -178,9 +178,8 @@ def main_sharded() -> None:
     Configurations C2-C5, total sizes fixed (strong scaling).  Every rank times its shard
     (CUDA events per launch, read-flushed L2, median of --iters launches); the slowest rank
     defines the time.  Aggregate GB/s = whole-tensor algorithmic bytes / that time; the
-    per-GPU fraction divides by N x the measured copy bandwidth.  Ops with an exchange: full
-    sum (partials exchanged inside the kernel over NVLink), mean along axis 0 (NCCL
-    all-reduce of [cols] floats, included in the time).
+    per-GPU fraction divides by N x the measured copy bandwidth.  Ops with an exchange (full
+    sum, mean along axis 0) exchange their per-GPU results inside the kernel over NVLink.
     """
     import os
 
@@ -271,11 +270,14 @@ def main_sharded() -> None:
     record("c3", "max axis 1", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_MAX))
     record("c3", "argmax axis 1 (int64)", 4 * R * C + 8 * R, lambda: capi.argmax_rows(X))
 
+    mean_out = torch.empty(C, dtype=torch.float32, device=dev)
+
     def mean0():
-        m = capi.reduce_cols(X, capi.REDUCE_MEAN, mean_divisor=R)
-        if world > 1:
-            dist.all_reduce(m)
-    record("c3", "mean axis 0 (+ all-reduce of [8192])", 4 * R * C + 4 * C * world, mean0)
+        if exchange is not None:
+            exchange.reduce_cols(X, capi.REDUCE_MEAN, R, mean_out)
+        else:
+            capi.reduce_cols(X, capi.REDUCE_MEAN, mean_divisor=R)
+    record("c3", "mean axis 0 (+ exchange)", 4 * R * C + 4 * C * world, mean0)
     record("c3", "full sum (+ exchange)", 4 * R * C + 4, lambda: total_sum(X))
     del X
     # C4

@@ -48,6 +48,28 @@ class CudaLocal:
         return capi.reduce_cols(x2d, capi.REDUCE_MEAN, mean_divisor=global_rows)
 
 
+class CudaFusedLocal:
+    """Shard-local compute with the exchange INSIDE the kernels (peer stores over NVLink):
+    results are already global, RowSharded must not reduce them again."""
+
+    fused = True
+
+    def __init__(self, exchange):
+        self.exchange = exchange
+
+    def full_sum_f64(self, x):
+        import torch
+        out64 = torch.empty(1, dtype=torch.float64, device=x.device)
+        self.exchange.sum(x.reshape(-1), None, out64)
+        return out64
+
+    def col_sums(self, x2d, global_rows):
+        import torch
+        from . import capi
+        out = torch.empty(x2d.shape[1], dtype=torch.float32, device=x2d.device)
+        return self.exchange.reduce_cols(x2d, capi.REDUCE_MEAN, global_rows, out)
+
+
 class RowSharded:
     """The two ops of the path that need an exchange, over a torch.distributed group."""
 
@@ -56,7 +78,7 @@ class RowSharded:
 
     def _all_reduce(self, t):
         import torch.distributed as dist
-        if self.shard.world > 1:
+        if self.shard.world > 1 and not getattr(self.local, "fused", False):
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 

@@ -155,8 +155,9 @@ int fdl_broadcast_binary_f32(const float* a, const float* b, float* out, int ndi
 int fdl_block_reduce_1024_f32(const float* x, float* out, int64_t n, int tree,
                               void* stream);
 
-/* Scratch bytes fdl_sum_f32 / fdl_reduce_cols_f32 need for the given problem.
- * Always a multiple of 256; the scratch pointer must be 256-byte aligned. */
+/* Scratch bytes fdl_sum_f32 / fdl_reduce_cols_f32 need for the given problem: a fixed
+ * 64 KiB region of arrival counters followed by the partial results.  Always a multiple of
+ * 256; the scratch pointer must be 256-byte aligned. */
 size_t fdl_sum_scratch_bytes(int64_t n);
 size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols);
 
@@ -165,7 +166,8 @@ size_t fdl_reduce_cols_scratch_bytes(int64_t batch, int64_t rows, int64_t cols);
  * Deterministic: same input, same launch -> same bits.  `scratch` may be NULL, in
  * which case the library uses a per-device workspace it allocates on first use and
  * keeps; otherwise it must hold fdl_sum_scratch_bytes(n), be 256-byte aligned, and have had
- * its first 256 bytes zeroed once (the kernel leaves them zero).  Calls that may overlap on
+ * its first 65,536 bytes zeroed once (the kernels leave them zero; the same buffer may then
+ * serve fdl_sum_f32 and fdl_reduce_cols_f32 calls of any shape).  Calls that may overlap on
  * the GPU (different streams) must not share scratch: pass each its own.  No counterpart in the
  * reference, whose reduction stops at one partial per 1024 elements
  * (src/kernels/cuda/reduction.cu:34-57). */
@@ -201,7 +203,7 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
  * A wait that runs out writes NaN to the outputs and raises the flag read by
  * fdl_take_device_error; it never hangs.
  *
- * Set-up, once per process: fdl_exchange_create (allocates this rank's 4 KiB buffer on the
+ * Set-up, once per process: fdl_exchange_create (allocates this rank's buffer, 4 KiB + 1 MiB per rank, on the
  * current device) -> fdl_exchange_local_handle (64-byte CUDA IPC handle) -> all-gather the
  * handles with any host mechanism -> fdl_exchange_connect(world * 64 bytes, rank order).
  * Calls are collective: every rank must call fdl_sum_allreduce_f32 the same number of
@@ -213,6 +215,16 @@ int fdl_exchange_connect(void* ctx, const unsigned char* handles);
 int fdl_exchange_destroy(void* ctx);
 int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx,
                           void* scratch, size_t scratch_bytes, void* stream);
+
+/* fdl_reduce_cols_f32 (one matrix) plus the exchange of the per-GPU [cols] results, in one
+ * kernel and with the same protocol: the CTA that finishes a block of columns sends each
+ * column's value to every rank as an 8-byte {float, epoch} peer store and folds all ranks'
+ * values in rank order.  x is this rank's [rows, cols] row block; for FDL_REDUCE_MEAN pass
+ * the GLOBAL row count as mean_divisor.  Every rank ends with the same out[cols].
+ * cols <= 65536.  Collective, same ordering rule as above. */
+int fdl_reduce_cols_allreduce_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,
+                                  double mean_divisor, void* ctx, void* scratch,
+                                  size_t scratch_bytes, void* stream);
 
 /* Row-wise reduction of a row-major [rows, cols] matrix along axis 1:
  * out[r] = op over c of x[r, c]; FDL_REDUCE_MAX ignores NaNs like fmaxf.  No counterpart

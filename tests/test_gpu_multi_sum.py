@@ -1,4 +1,5 @@
-"""Two GPUs: the fused sum + exchange kernel against per-GPU sums added on the host.
+"""Two GPUs: the fused sum + exchange and column-reduction + exchange kernels against
+per-GPU results combined on the host.
 Skipped on boxes with a single GPU.  Ranks are separate processes (one per GPU); the
 64-byte IPC handles travel over a gloo group."""
 import os
@@ -41,10 +42,47 @@ def _worker(rank, world, port, n, out):
             ex.sum(x, o32, o64)
             torch.cuda.synchronize()
             results.append(o64.item())
+        # column reductions with the exchange in the kernel: mean over ALL rows of the stacked
+        # [world * rows, cols] matrix, and the column maxima
+        cols_ok = True
+        for rows, cols in ((300, 256), (1000, 8192), (64, 36), (5000, 65536)):
+            shard = torch.from_numpy(rng.normal(size=(rows, cols)).astype(np.float32)).cuda()
+            local_sum = shard.double().sum(dim=0).cpu()
+            local_max = shard.max(dim=0).values.cpu()
+            sums = [torch.zeros(cols, dtype=torch.float64) for _ in range(world)]
+            maxs = [torch.zeros(cols, dtype=torch.float32) for _ in range(world)]
+            dist.all_gather(sums, local_sum)
+            dist.all_gather(maxs, local_max)
+            want_mean = (sum(sums) / (world * rows)).numpy()
+            want_max = torch.stack(maxs).max(dim=0).values.numpy()
+            res = torch.empty(cols, dtype=torch.float32, device="cuda")
+            for _ in range(3):
+                ex.reduce_cols(shard, capi.REDUCE_MEAN, world * rows, res)
+                torch.cuda.synchronize()
+                got = res.cpu().numpy()
+                good = bool(np.allclose(got, want_mean, rtol=1e-5, atol=1e-6))
+                if not good:
+                    print(f"rank {rank}: mean [{rows},{cols}] max abs err {np.abs(got - want_mean).max():.3e}", flush=True)
+                cols_ok &= good
+            ex.reduce_cols(shard, capi.REDUCE_MAX, 1, res)
+            torch.cuda.synchronize()
+            good = bool(np.array_equal(res.cpu().numpy(), want_max))
+            if not good:
+                print(f"rank {rank}: max [{rows},{cols}] differs in {(res.cpu().numpy() != want_max).sum()} columns", flush=True)
+            cols_ok &= good
+            gathered_out = [torch.zeros(cols) for _ in range(world)]
+            dist.all_gather(gathered_out, res.cpu())
+            good = all(torch.equal(g, gathered_out[0]) for g in gathered_out)   # same bits on every rank
+            if not good:
+                print(f"rank {rank}: [{rows},{cols}] ranks disagree", flush=True)
+            cols_ok &= good
         capi.take_device_error()
         dist.barrier()
         ex.close()
-        ok = all(r == want for r in results) and np.float32(want) == o32.item()
+        sum_ok = all(r == want for r in results) and np.float32(want) == o32.item()
+        if not sum_ok:
+            print(f"rank {rank}: sum results {results} want {want}", flush=True)
+        ok = sum_ok and cols_ok
         gathered = [None] * world
         dist.all_gather_object(gathered, (ok, results[0]))
         if rank == 0:

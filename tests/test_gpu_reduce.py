@@ -113,6 +113,20 @@ def test_column_reductions(fdl, cuda, rows, cols):
     assert_bit_exact(again, to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "deterministic")
 
 
+def test_column_reductions_of_changing_shapes_share_the_workspace(fdl, cuda):
+    """Back-to-back calls whose scratch layouts differ (more column blocks, fewer groups, and the
+    full sum in between) must not see each other's leftovers in the arrival counters."""
+    rng = np.random.default_rng(5)
+    for rows, cols in [(5000, 32768), (1000, 65536), (300, 256), (1000, 65536), (100, 65536), (2000, 16384)]:
+        x = rng.normal(size=(rows, cols)).astype(np.float32)
+        xd = dev(cuda, x)
+        norm = np.sqrt((x.astype(np.float64) ** 2).sum(axis=0)) / rows
+        for _ in range(2):
+            assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN)), orc.reduce_cols(x, 1), norm, f"{rows}x{cols}")
+            fdl.full_sum(xd)
+        assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX)), orc.reduce_cols(x, 2), "col max")
+
+
 def test_column_reduction_batched_and_caller_scratch(fdl, cuda):
     rng = np.random.default_rng(3)
     x = rng.normal(size=(5, 700, 96)).astype(np.float32)
