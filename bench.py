@@ -270,7 +270,7 @@ def run_ours(args) -> None:
     sum32 = torch.zeros(1, dtype=torch.float32, device=dev)
     sum64 = torch.zeros(1, dtype=torch.float64, device=dev)
     exchange = None
-    if world > 1 and args.allreduce == "fused":
+    if world > 1 and args.allreduce in ("fused", "split"):
         def gather(handle: bytes):
             handles = [None] * world
             dist.all_gather_object(handles, handle)
@@ -281,23 +281,58 @@ def run_ours(args) -> None:
     stream = torch.cuda.current_stream().cuda_stream
     lib = capi.lib()
 
-    def step(events=None):
-        if events is not None:
-            events[0].record()
-        capi.binary(a, b, capi.ADD, out=c)
-        if events is not None:
-            events[1].record()
-        capi.broadcast_binary(d2, row2, capi.ADD, out=e2)
-        if events is not None:
-            events[2].record()
+    split = exchange is not None and args.allreduce == "split"
+
+    # The timed loop calls the C ABI with arguments converted once: at 8 GPUs a step is ~150 us
+    # and per-call Python work (tensor checks, shape arithmetic) would otherwise rival it.
+    import ctypes as C
+    ADD = capi.ADD
+    pa, pb, pc, pd, pe, pf, prow = (t.data_ptr() for t in (a, b, c, d, e, f, row))
+    p32, p64 = sum32.data_ptr(), sum64.data_ptr()
+    i64x2 = C.c_int64 * 2
+    bshape, bstr_a, bstr_row = i64x2(rows, COLS), i64x2(COLS, 1), i64x2(0, 1)
+    xctx = exchange.ctx if exchange is not None else None
+
+    def must(status, where):
+        if status != 0:
+            capi.check(status, where)
+
+    def op_add():
+        must(lib.fdl_binary_f32(pa, pb, pc, n, ADD, stream), "fdl_binary_f32")
+
+    def op_broadcast():
+        must(lib.fdl_broadcast_binary_f32(pd, prow, pe, 2, bshape, bstr_a, bstr_row, ADD, stream),
+             "fdl_broadcast_binary_f32")
+
+    def op_sum():
         if exchange is not None:
             # sum + exchange of the per-GPU partials over NVLink in ONE kernel
-            exchange.sum(f, sum32, sum64)
+            must(lib.fdl_sum_allreduce_f32(pf, n, p32, p64, xctx, None, 0, stream), "fdl_sum_allreduce_f32")
         else:
-            capi.check(lib.fdl_sum_f32(f.data_ptr(), n, sum32.data_ptr(), sum64.data_ptr(), None, 0, stream),
-                       "fdl_sum_f32")
+            must(lib.fdl_sum_f32(pf, n, p32, p64, None, 0, stream), "fdl_sum_f32")
+
+    def op_sum_start():
+        must(lib.fdl_sum_allreduce_start_f32(pf, n, xctx, None, 0, stream), "fdl_sum_allreduce_start_f32")
+
+    def op_sum_finish():
+        must(lib.fdl_sum_allreduce_finish_f32(p32, p64, xctx, stream), "fdl_sum_allreduce_finish_f32")
+
+    if split:
+        # The three ops of a step are independent, so the sum goes first: its kernel sends the
+        # rank's partial to all ranks and returns; the add and the broadcast add run while the
+        # partials cross NVLink and slower ranks catch up; a one-warp kernel folds them last.
+        plan = [("sum", op_sum_start), ("add", op_add), ("broadcast_add", op_broadcast), ("sum", op_sum_finish)]
+    else:
+        plan = [("add", op_add), ("broadcast_add", op_broadcast), ("sum", op_sum)]
+    launches_per_step = len(plan)
+
+    def step(events=None):
+        for i, (_, fn) in enumerate(plan):
+            if events is not None:
+                events[i].record()
+            fn()
         if events is not None:
-            events[3].record()
+            events[len(plan)].record()
         if world > 1 and exchange is None:
             dist.all_reduce(sum64)  # per-GPU partials -> global sum: same stream, no host round trip
 
@@ -313,19 +348,22 @@ def run_ours(args) -> None:
 
     # ---- timed region: exactly K steps ---------------------------------------------------------
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(plan) + 1)] for _ in range(K)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     sampler.start()
     barrier()
     start.record()
+    t_host = time.perf_counter()
     for k in range(K):
         step(ev[k])
     stop.record()
+    enqueue_us = (time.perf_counter() - t_host) * 1e6 / K   # host time to enqueue a step (no sync inside)
     barrier()
     clocks = sampler.stop()
     ms_total = start.elapsed_time(stop)
-    per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)) / K for i in range(3)]
+    per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K) for i, (name, _) in enumerate(plan)
+                  if name == which) / K for which in ("add", "broadcast_add", "sum")]
 
     # ---- end to end: host tensors in, host results out, through the C ABI ------------------------
     need_host = not args.no_e2e or (rank == 0 and world == 1 and not args.no_cpu)
@@ -358,10 +396,11 @@ def run_ours(args) -> None:
         e2e_sec = (time.perf_counter() - t0) / e2e_steps
 
     # ---- reduce over ranks: the slowest rank defines the time --------------------------------------
-    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op], dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op, enqueue_us], dtype=torch.float64,
+                         device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms_total, e2e_sec, t_add, t_bc, t_sum = stats.tolist()
+    ms_total, e2e_sec, t_add, t_bc, t_sum, enqueue_us = stats.tolist()
 
     total_bytes = sum(algorithmic_bytes(args.rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
     value = total_bytes * K / (ms_total * 1e-3) / 1e9
@@ -381,6 +420,8 @@ def run_ours(args) -> None:
                    "partition": f"leading dimension over {world} GPU(s): {rows} of {args.rows} rows on rank 0",
                    "l2": "inputs larger than L2 (six distinct tensors stream per step)",
                    "full_sum_exchange": ("none (1 GPU)" if world == 1 else
+                                         "split: the sum kernel sends the partial over NVLink (peer stores), the "
+                                         "other two ops overlap the exchange, a one-warp kernel folds" if split else
                                          "fused into the sum kernel (peer stores over NVLink)" if exchange is not None
                                          else "NCCL all-reduce of one double")},
         "clocks": clocks,
@@ -388,7 +429,8 @@ def run_ours(args) -> None:
                 "h2d_bytes_per_step": (2 * args.rows * COLS + world * COLS) * 4,
                 "d2h_bytes_per_step": 2 * args.rows * COLS * 4 + 8 * world, "steps": e2e_steps,
                 "api": "fdl_host_sweep_f32 (pinned host tensors in, host results out)"},
-        "gpu_launches": 3 * K * world,
+        "gpu_launches": launches_per_step * K * world,
+        "host_enqueue_us_per_step": enqueue_us,
         "roofline": {"bound": "hbm", "kernel": "map_kernel<4,2,4,AddFn> (binary add)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                      "traffic": traffic_per_launch(big["add"])},
@@ -428,9 +470,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
+    ap.add_argument("--allreduce", choices=["fused", "split", "nccl"], default="fused",
                     help="N > 1: exchange the full-sum partials inside the sum kernel over NVLink peer stores "
-                         "(fused) or with a separate NCCL all-reduce (nccl)")
+                         "in one call (fused), in two halves with the other ops of the step between them "
+                         "(split), or with a separate NCCL all-reduce (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--rows", type=int, default=ROWS,

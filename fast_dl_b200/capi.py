@@ -46,6 +46,8 @@ PROTOTYPES = {
     "fdl_exchange_connect": (_int, [_vp, C.c_char_p]),
     "fdl_exchange_destroy": (_int, [_vp]),
     "fdl_sum_allreduce_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fdl_sum_allreduce_start_f32": (_int, [_vp, _i64, _vp, _vp, _sz, _vp]),
+    "fdl_sum_allreduce_finish_f32": (_int, [_vp, _vp, _vp, _vp]),
     "fdl_reduce_cols_allreduce_f32": (_int, [_vp, _i64, _i64, _vp, _int, _f64, _vp, _vp, _sz, _vp]),
     "fdl_reduce_rows_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
     "fdl_argmax_rows_f32": (_int, [_vp, _i64, _i64, _vp, _vp]),
@@ -387,6 +389,16 @@ class Exchange:
     def sum(self, x, out32, out64):
         check(lib().fdl_sum_allreduce_f32(_ptr(x), x.numel(), _ptr(out32), _ptr(out64), self.ctx, None, 0,
                                           _stream()), "fdl_sum_allreduce_f32")
+
+    def sum_start(self, x):
+        """First half: the sum kernel sends this rank's partial to all ranks and does not wait."""
+        check(lib().fdl_sum_allreduce_start_f32(_ptr(x), x.numel(), self.ctx, None, 0, _stream()),
+              "fdl_sum_allreduce_start_f32")
+
+    def sum_finish(self, out32, out64):
+        """Second half: fold all ranks' partials (rank order) into the outputs."""
+        check(lib().fdl_sum_allreduce_finish_f32(_ptr(out32), _ptr(out64), self.ctx, _stream()),
+              "fdl_sum_allreduce_finish_f32")
 
     def reduce_cols(self, x2d, op, mean_divisor, out):
         rows, cols = x2d.shape

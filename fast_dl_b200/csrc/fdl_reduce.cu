@@ -201,6 +201,7 @@ constexpr unsigned long long kExchangeWaitNs = 2000000000ull;  // 2 s, then give
 struct SumExchange {
     int world = 0;  // 0: single GPU, no exchange
     int rank = 0;
+    int send_only = 0;  // 1: split-phase start -- send the partial, leave waiting to the finish kernel
     unsigned int epoch = 0;
     unsigned long long* words[kMaxRanks] = {};  // each rank's buffer
     unsigned int* error_flag = nullptr;
@@ -251,6 +252,65 @@ __device__ __forceinline__ float exchange_column(const ColsExchange& xc, int64_t
         acc = R::combine(acc, __uint_as_float(static_cast<unsigned int>(w >> 32)));
     }
     return acc;
+}
+
+
+// Sends this rank's partial to rank `peer`: two indivisible 8-byte stores, each carrying
+// the epoch, into entry [epoch&1][rank] of the peer's buffer.
+__device__ __forceinline__ void exchange_send_partial(const SumExchange& xc, int peer, double value) {
+    const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks * 2;
+    const unsigned long long tag = xc.epoch;
+    const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(value));
+    volatile unsigned long long* dst = xc.words[peer] + par + 2 * xc.rank;
+    dst[0] = ((bits >> 32) << 32) | tag;
+    dst[1] = ((bits & 0xffffffffull) << 32) | tag;
+}
+
+// Waits (bounded) until every rank's partial of this epoch has arrived in this rank's own
+// buffer and adds them in rank order; result valid in thread 0.  Called by all threads of a
+// CTA of at least kMaxRanks threads.  A wait that runs out gives NaN and raises the flag.
+__device__ __forceinline__ double exchange_fold_partials(const SumExchange& xc) {
+    __shared__ double gathered[kMaxRanks];
+    const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks * 2;
+    const unsigned long long tag = xc.epoch;
+    bool ok = true;
+    if (threadIdx.x < xc.world) {
+        volatile unsigned long long* src = xc.words[xc.rank] + par + 2 * threadIdx.x;
+        const unsigned long long t0 = global_timer_ns();
+        unsigned long long w0 = src[0], w1 = src[1];
+        unsigned int polls = 0;
+        while ((w0 & 0xffffffffull) != tag || (w1 & 0xffffffffull) != tag) {
+            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
+                ok = false;
+                break;
+            }
+            w0 = src[0];
+            w1 = src[1];
+        }
+        gathered[threadIdx.x] = __longlong_as_double(static_cast<long long>(((w0 >> 32) << 32) | (w1 >> 32)));
+    }
+    ok = __syncthreads_and(ok);
+    double total = 0.0;
+    if (threadIdx.x == 0) {
+        if (ok) {
+            for (int q = 0; q < xc.world; ++q) total += gathered[q];  // rank order
+        } else {
+            total = nan("");
+            atomicOr(xc.error_flag, 2u);
+        }
+    }
+    return total;
+}
+
+// Second half of the split-phase exchange: one warp folds the partials that the ranks'
+// sum kernels sent (send_only) and writes the results.
+__global__ void __launch_bounds__(kWarp) sum_exchange_finish_kernel(float* out_f32, double* out_f64,
+                                                                  const SumExchange xc) {
+    const double total = exchange_fold_partials(xc);
+    if (threadIdx.x == 0) {
+        if (out_f32 != nullptr) *out_f32 = static_cast<float>(total);
+        if (out_f64 != nullptr) *out_f64 = total;
+    }
 }
 
 template <int CL, bool VEC>
@@ -348,44 +408,12 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
         __shared__ double my_total;
         if (threadIdx.x == 0) my_total = total;
         __syncthreads();
-        const int par = static_cast<int>(xc.epoch & 1u) * kMaxRanks * 2;
-        const unsigned long long tag = xc.epoch;
-        bool ok = true;
-        double from_peer = 0.0;
-        if (threadIdx.x < xc.world) {
-            const int peer = threadIdx.x;
-            // Send to `peer`: two indivisible 8-byte stores, each carrying the epoch.
-            const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(my_total));
-            volatile unsigned long long* dst = xc.words[peer] + par + 2 * xc.rank;
-            dst[0] = ((bits >> 32) << 32) | tag;
-            dst[1] = ((bits & 0xffffffffull) << 32) | tag;
-            // Receive `peer`'s value from this rank's own buffer.
-            volatile unsigned long long* src = xc.words[xc.rank] + par + 2 * peer;
-            const unsigned long long t0 = global_timer_ns();
-            unsigned long long w0 = src[0], w1 = src[1];
-            unsigned int polls = 0;
-            while ((w0 & 0xffffffffull) != tag || (w1 & 0xffffffffull) != tag) {
-                if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
-                    ok = false;
-                    break;
-                }
-                w0 = src[0];
-                w1 = src[1];
-            }
-            from_peer = __longlong_as_double(static_cast<long long>(((w0 >> 32) << 32) | (w1 >> 32)));
+        if (threadIdx.x < xc.world) exchange_send_partial(xc, threadIdx.x, my_total);
+        if (xc.send_only) {
+            if (threadIdx.x == 0) *counter = 0;
+            return;
         }
-        __shared__ double gathered[kMaxRanks];
-        if (threadIdx.x < xc.world) gathered[threadIdx.x] = from_peer;
-        ok = __syncthreads_and(ok);
-        if (threadIdx.x == 0) {
-            if (ok) {
-                total = 0.0;
-                for (int q = 0; q < xc.world; ++q) total += gathered[q];  // rank order
-            } else {
-                total = nan("");
-                atomicOr(xc.error_flag, 2u);
-            }
-        }
+        total = exchange_fold_partials(xc);
     }
     if (threadIdx.x == 0) {
         if (out_f32 != nullptr) *out_f32 = static_cast<float>(total);
@@ -1095,6 +1123,7 @@ struct ExchangeContext {
     int device = 0;
     unsigned int epoch = 0;      // full-sum exchanges so far
     unsigned int epoch_cols = 0; // column-vector exchanges so far
+    bool sum_pending = false;    // a split-phase full sum has started and not finished
     void* local = nullptr;
     void* peer[kMaxRanks] = {};
     bool connected = false;
@@ -1162,11 +1191,19 @@ int fdl_exchange_destroy(void* ctx_in) {
     return FDL_OK;
 }
 
-int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx_in,
-                          void* scratch, size_t scratch_bytes, void* stream) {
-    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
-    if (ctx == nullptr || !ctx->connected) return FDL_ERR_INVALID_ARGUMENT;
-    if (n < 0 || (out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
+static int sum_exchange_fill(ExchangeContext* ctx, SumExchange* xc) {
+    xc->world = ctx->world;
+    xc->rank = ctx->rank;
+    xc->epoch = ctx->epoch;
+    for (int p = 0; p < ctx->world; ++p) xc->words[p] = static_cast<unsigned long long*>(ctx->peer[p]);
+    return error_flag_device_ptr(&xc->error_flag);
+}
+
+static int sum_allreduce_launch(const float* x, int64_t n, float* out_f32, double* out_f64,
+                                ExchangeContext* ctx, void* scratch, size_t scratch_bytes, void* stream,
+                                bool send_only) {
+    if (ctx == nullptr || !ctx->connected || ctx->sum_pending) return FDL_ERR_INVALID_ARGUMENT;
+    if (n < 0 || (!send_only && out_f32 == nullptr && out_f64 == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
     if (n > 0 && x == nullptr) return FDL_ERR_INVALID_ARGUMENT;
     int status = FDL_OK;
     const size_t need = fdl_sum_scratch_bytes(n);
@@ -1176,20 +1213,45 @@ int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out
     } else if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) {
         return FDL_ERR_WORKSPACE;
     }
-    SumExchange xc;
-    xc.world = ctx->world;
-    xc.rank = ctx->rank;
     ctx->epoch += 1;
     if (ctx->epoch == 0) ctx->epoch = 1;  // 0 is the buffers' initial state
-    xc.epoch = ctx->epoch;
-    for (int p = 0; p < ctx->world; ++p) xc.words[p] = static_cast<unsigned long long*>(ctx->peer[p]);
-    status = error_flag_device_ptr(&xc.error_flag);
+    SumExchange xc;
+    status = sum_exchange_fill(ctx, &xc);
     if (status != FDL_OK) return status;
+    xc.send_only = send_only ? 1 : 0;
     unsigned int* counter = static_cast<unsigned int*>(scratch);
     double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kCounterBytes);
     cudaStream_t s = as_stream(stream);
-    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s, xc);
-    return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s, xc);
+    status = aligned16(x) ? launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s, xc)
+                          : launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s, xc);
+    if (status == FDL_OK && send_only) ctx->sum_pending = true;
+    return status;
+}
+
+int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx_in,
+                          void* scratch, size_t scratch_bytes, void* stream) {
+    return sum_allreduce_launch(x, n, out_f32, out_f64, static_cast<ExchangeContext*>(ctx_in), scratch,
+                                scratch_bytes, stream, false);
+}
+
+int fdl_sum_allreduce_start_f32(const float* x, int64_t n, void* ctx_in, void* scratch, size_t scratch_bytes,
+                                void* stream) {
+    return sum_allreduce_launch(x, n, nullptr, nullptr, static_cast<ExchangeContext*>(ctx_in), scratch,
+                                scratch_bytes, stream, true);
+}
+
+int fdl_sum_allreduce_finish_f32(float* out_f32, double* out_f64, void* ctx_in, void* stream) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || !ctx->connected || !ctx->sum_pending) return FDL_ERR_INVALID_ARGUMENT;
+    if (out_f32 == nullptr && out_f64 == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    SumExchange xc;
+    const int status = sum_exchange_fill(ctx, &xc);
+    if (status != FDL_OK) return status;
+    sum_exchange_finish_kernel<<<1, kWarp, 0, as_stream(stream)>>>(out_f32, out_f64, xc);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ctx->sum_pending = false;
+    return FDL_OK;
 }
 
 int fdl_reduce_cols_allreduce_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,

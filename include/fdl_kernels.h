@@ -216,6 +216,21 @@ int fdl_exchange_destroy(void* ctx);
 int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx,
                           void* scratch, size_t scratch_bytes, void* stream);
 
+/* The same exchange in two halves, so that other work can run while the partials cross
+ * NVLink and while slower ranks catch up.  fdl_sum_allreduce_start_f32 launches the sum
+ * kernel, whose last CTA sends this rank's partial to every rank and returns without
+ * waiting; fdl_sum_allreduce_finish_f32 launches a one-warp kernel that waits (at most two
+ * seconds, then NaN + the device-error flag) for all ranks' partials of that exchange and
+ * adds them in rank order - the same bits as fdl_sum_allreduce_f32 on every rank.  Kernels
+ * enqueued on `stream` between the two calls overlap the exchange.  Per context, start and
+ * finish must alternate (a second start, or fdl_sum_allreduce_f32, before the finish returns
+ * FDL_ERR_INVALID_ARGUMENT, as does a finish with nothing started); both halves of one
+ * exchange go to the same stream, or to streams the caller has ordered.  Collective, same
+ * ordering rule as above.  No counterpart in the reference. */
+int fdl_sum_allreduce_start_f32(const float* x, int64_t n, void* ctx, void* scratch,
+                                size_t scratch_bytes, void* stream);
+int fdl_sum_allreduce_finish_f32(float* out_f32, double* out_f64, void* ctx, void* stream);
+
 /* fdl_reduce_cols_f32 (one matrix) plus the exchange of the per-GPU [cols] results, in one
  * kernel and with the same protocol: the CTA that finishes a block of columns sends each
  * column's value to every rank as an 8-byte {float, epoch} peer store and folds all ranks'

@@ -42,6 +42,31 @@ def _worker(rank, world, port, n, out):
             ex.sum(x, o32, o64)
             torch.cuda.synchronize()
             results.append(o64.item())
+        # the same exchange in two halves, with other work on the stream in between, mixed
+        # with the one-call form (the epochs and parities are shared)
+        other = torch.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)).cuda()
+        for k in range(6):
+            o64.zero_()
+            ex.sum_start(x)
+            capi.binary(other, x, capi.ADD)           # overlaps the exchange
+            if k == 2:
+                try:                                    # a second start before the finish is refused
+                    ex.sum_start(x)
+                    results.append(float("nan"))
+                except capi.FdlError:
+                    pass
+            ex.sum_finish(o32, o64)
+            torch.cuda.synchronize()
+            results.append(o64.item())
+            if k % 2:
+                ex.sum(x, o32, o64)
+                torch.cuda.synchronize()
+                results.append(o64.item())
+        try:                                            # a finish with nothing started is refused
+            ex.sum_finish(o32, o64)
+            results.append(float("nan"))
+        except capi.FdlError:
+            pass
         # column reductions with the exchange in the kernel: mean over ALL rows of the stacked
         # [world * rows, cols] matrix, and the column maxima
         cols_ok = True
