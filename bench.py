@@ -354,11 +354,17 @@ def run_ours(args) -> None:
     sampler.start()
     barrier()
     start.record()
+    # Host time to enqueue a step, over the first steps only: later the driver's launch queue
+    # is full and the host waits for the GPU, which says nothing about the host.
+    k_host = min(K, 100)
     t_host = time.perf_counter()
     for k in range(K):
+        if k == k_host:
+            enqueue_us = (time.perf_counter() - t_host) * 1e6 / k_host
         step(ev[k])
     stop.record()
-    enqueue_us = (time.perf_counter() - t_host) * 1e6 / K   # host time to enqueue a step (no sync inside)
+    if K == k_host:
+        enqueue_us = (time.perf_counter() - t_host) * 1e6 / k_host
     barrier()
     clocks = sampler.stop()
     ms_total = start.elapsed_time(stop)
@@ -368,7 +374,7 @@ def run_ours(args) -> None:
     # ---- end to end: host tensors in, host results out, through the C ABI ------------------------
     need_host = not args.no_e2e or (rank == 0 and world == 1 and not args.no_cpu)
     host = None
-    e2e_steps, e2e_sec = 0, float("nan")
+    e2e_steps, e2e_sec, link_sec = 0, float("nan"), 0.0
     if need_host:
         del c, e, d, f
         torch.cuda.empty_cache()
@@ -395,12 +401,33 @@ def run_ours(args) -> None:
         barrier()
         e2e_sec = (time.perf_counter() - t0) / e2e_steps
 
+        # What the host link itself gives on this box, for the e2e figure to be read against:
+        # x up and z down as two plain pinned copies running at the same time (all ranks at once).
+        up_dst = torch.empty_like(hx, device=dev)
+        down_src = torch.empty_like(hx, device=dev).fill_(1.0)
+        s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+
+        def duplex_copy():
+            with torch.cuda.stream(s_up):
+                up_dst.copy_(hx, non_blocking=True)
+            with torch.cuda.stream(s_down):
+                hz.copy_(down_src, non_blocking=True)
+
+        duplex_copy()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            duplex_copy()
+        barrier()
+        link_sec = (time.perf_counter() - t0) / 3
+        del up_dst, down_src
+
     # ---- reduce over ranks: the slowest rank defines the time --------------------------------------
-    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op, enqueue_us], dtype=torch.float64,
-                         device=dev)
+    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op, enqueue_us, link_sec],
+                         dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms_total, e2e_sec, t_add, t_bc, t_sum, enqueue_us = stats.tolist()
+    ms_total, e2e_sec, t_add, t_bc, t_sum, enqueue_us, link_sec = stats.tolist()
 
     total_bytes = sum(algorithmic_bytes(args.rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
     value = total_bytes * K / (ms_total * 1e-3) / 1e9
@@ -428,7 +455,13 @@ def run_ours(args) -> None:
         "e2e": {"value": (total_bytes / e2e_sec / 1e9) if e2e_steps else None, "unit": "GB/s",
                 "h2d_bytes_per_step": (2 * args.rows * COLS + world * COLS) * 4,
                 "d2h_bytes_per_step": 2 * args.rows * COLS * 4 + 8 * world, "steps": e2e_steps,
-                "api": "fdl_host_sweep_f32 (pinned host tensors in, host results out)"},
+                "api": "fdl_host_sweep_f32 (pinned host tensors in, host results out)",
+                # e2e moves 2 tensors up and 2 down per step; the link line is one up + one down at once
+                "link": (None if not link_sec else {
+                    "duplex_GBps_per_direction": args.rows * COLS * 4 / link_sec / 1e9,
+                    "floor_ms_per_step": 2 * link_sec * 1e3,
+                    "frac_of_link_floor": 2 * link_sec / e2e_sec,
+                    "what": "plain pinned copies of one tensor up and one down at the same time, all ranks"})},
         "gpu_launches": launches_per_step * K * world,
         "host_enqueue_us_per_step": enqueue_us,
         "roofline": {"bound": "hbm", "kernel": "map_kernel<4,2,4,AddFn> (binary add)", "achieved": achieved,
