@@ -88,6 +88,17 @@ def main(ref=None) -> None:
         print(f"{config:3s} {op:34s} {med * 1e3:9.1f} us {row['GBps']:8.1f} GB/s  {100 * row['frac_of_measured_peak']:5.1f}%{extra}",
               flush=True)
 
+    def graphed(fn):
+        """fn captured into a CUDA graph (after an eager pass: first uses allocate); returns the replay."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        keep.append(graph)
+        return graph.replay
+
+    keep = []
     cfgs = args.configs.split(",")
 
     if "c1" in cfgs:
@@ -107,6 +118,7 @@ def main(ref=None) -> None:
             ref.gpu_activation(t2.data_ptr(), out.data_ptr(), n, 0)
 
         record("c1", "unfused mul, add, relu (3 launches)", 32 * n, unfused, ref_unfused if ref else None)
+        record("c1", "the same 3 launches replayed from a CUDA graph", 32 * n, graphed(unfused))
 
     if "c2" in cfgs:
         R = C = 4096
