@@ -19,6 +19,13 @@
  *     the launch; a negative value is one of the FDL_ERR_* codes below.  Nothing
  *     throws and nothing falls back to a CPU path.
  *   - Launches are asynchronous with respect to the host, like the reference's.
+ *   - Stream capture: the device-pointer entry points enqueue kernels on `stream` and
+ *     nothing else, so a chain of them can be captured into a CUDA graph and replayed.
+ *     An op's first use on a device may allocate the library's workspace, so run the
+ *     chain once eagerly (or pass your own scratch) before the capture begins.  The
+ *     cross-GPU entry points (fdl_*_allreduce_*) pass a per-call epoch as a kernel
+ *     argument and must not be captured; the fdl_host_* family synchronises internally
+ *     and cannot be.
  *   - Element counts are int64_t.  The reference takes `int`/`size_t`; the C++
  *     shims in dl::kernels keep those narrower types and widen here.
  */
