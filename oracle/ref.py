@@ -41,9 +41,9 @@ def hardware_threads() -> int:
 
 # ---- CPU: the reference's check functions ----------------------------------------------------
 
-def cpu_activation(x, op, alpha=0.01, threads=1):
+def cpu_activation(x, op, alpha=0.01, threads=1, out=None):
     x, px = _f(x)
-    out = np.empty_like(x)
+    out = np.empty_like(x) if out is None else out
     lib().ref_cpu_activation_mt(px, out.ctypes.data_as(_fp), _sz(x.size), C.c_int(op), C.c_float(alpha),
                                 C.c_int(threads))
     return out
