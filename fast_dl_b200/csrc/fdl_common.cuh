@@ -45,6 +45,7 @@ struct Tuning {
     int cols_tx = 64;            // column reduction: threads across columns per CTA (16..256)
     int cols_cluster = 4;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8)
     int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
+    int cols_chunks = 0;         // column reduction: row chunks per column block (0 = derived)
     int rows_staged = 0;   // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA
 };
 Tuning& tuning();

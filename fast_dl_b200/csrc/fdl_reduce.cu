@@ -848,6 +848,7 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     const int64_t target = static_cast<int64_t>(sm_count) * tuning().cols_ctas_per_sm;
     int64_t chunks = ceil_div(target, static_cast<int64_t>(g->col_blocks) * batch);
     const int64_t max_chunks = ceil_div(rows, static_cast<int64_t>(ty) * 32);
+    if (tuning().cols_chunks > 0) chunks = tuning().cols_chunks;
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks < 1) chunks = 1;
     if (chunks > 65535) chunks = 65535;
