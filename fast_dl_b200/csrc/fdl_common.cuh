@@ -19,6 +19,8 @@ constexpr unsigned kFullMask = 0xffffffffu;
 
 // ---- host side -----------------------------------------------------------------------
 
+constexpr int kMaxDevicesTracked = 64;  // per-device bookkeeping arrays (device index modulo this)
+
 struct DeviceInfo {
     int device = -1;
     int sm_count = 0;
@@ -46,7 +48,8 @@ struct Tuning {
     int cols_cluster = 4;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8)
     int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
     int cols_chunks = 0;         // column reduction: row chunks per column block (0 = derived)
-    int rows_staged = 0;   // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA
+    int rows_staged = -1;  // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA,
+                           // -1 = staged for rows of up to 128 floats, direct beyond
 };
 Tuning& tuning();
 

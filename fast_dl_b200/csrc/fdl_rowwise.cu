@@ -6,7 +6,8 @@
 // fixed group of rows and the hardware block scheduler spreads the CTAs over the SMs.
 //
 // Two ways of bringing a row in are built, selected by fdl_set_tuning("rows_staged", v):
-//   v = 0 (default)  direct: each thread issues all its 128-bit global loads at once;
+//   v = -1 (default) staged for rows of up to 128 floats, direct for longer ones;
+//   v = 0            direct: each thread issues all its 128-bit global loads at once;
 //   v = 1            staged: thread 0 issues ONE bulk-async copy (cp.async.bulk on an
 //                    mbarrier, non-multicast) for the CTA's whole span of rows into shared
 //                    memory, and the teams read their rows from there.
@@ -14,7 +15,9 @@
 // lengths 256..16384, the staged form 92-101%, and a persistent per-team ring of bulk
 // copies (removed) 81-90%: with this little arithmetic per byte, enough resident warps
 // already keep the memory system full, and the staged form pays an extra trip through
-// shared memory plus a CTA-wide wait.  The staged form stays selectable so the
+// shared memory plus a CTA-wide wait.  Rows of up to 128 floats are the exception: there a
+// thread of the direct form has one load in flight and measures 76-90%, the staged form
+// 97-98%, so the default picks by row length.  Both forms stay selectable so the
 // comparison can be repeated on the same build.
 //
 // Rows that are unaligned, not a multiple of 4 floats, or longer than 16384 floats take a
@@ -339,13 +342,15 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
     const size_t smem = static_cast<size_t>(kTeams) * rpt * row_bytes;
     if (smem + 1024 > static_cast<size_t>(info->max_smem_optin)) return FDL_ERR_UNSUPPORTED;
     auto kernel = rows_staged_kernel<Op, TPR, TH, NV>;
-    static size_t configured_smem = 48 * 1024 - 256;
-    if (smem > configured_smem) {
+    // The attribute belongs to the device, so what has been configured is kept per device.
+    static size_t configured_smem[kMaxDevicesTracked] = {};
+    size_t& configured = configured_smem[info->device % kMaxDevicesTracked];
+    if (smem > 48 * 1024 - 256 && smem > configured) {
         // Exactly what is needed: the opt-in ceiling covers static + dynamic together.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        configured_smem = smem;
+        configured = smem;
     }
     const int64_t grid = ceil_div(p.rows, static_cast<int64_t>(kTeams) * rpt);
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
@@ -369,6 +374,13 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
         return LAUNCH<Op, 512, 512, 8>(p, info, stream);                                 \
     } while (0)
 
+constexpr int64_t kStagedAutoMaxCols = 128;
+
+template <class Op>
+int dispatch_rows_staged(const RowParams& p, const DeviceInfo* info, cudaStream_t stream) {
+    FDL_ROW_DISPATCH(launch_staged_cfg);
+}
+
 template <class Op>
 int launch_rows_op(RowParams p, cudaStream_t stream) {
     if (p.rows < 0 || p.cols < 0) return FDL_ERR_INVALID_ARGUMENT;
@@ -384,7 +396,14 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
                               aligned16(p.y) && (p.gamma == nullptr || aligned16(p.gamma)) &&
                               (p.beta == nullptr || aligned16(p.beta));
     if (in_registers) {
-        if (tuning().rows_staged != 0) FDL_ROW_DISPATCH(launch_staged_cfg);
+        // -1 (default): staged for rows of up to 128 floats, where a thread of the direct
+        // form has a single load in flight (measured 97-98% of the copy bandwidth staged
+        // against 76-90% direct; from 256 floats on the direct form leads, 104-107%).
+        const int mode = tuning().rows_staged;
+        if (mode == 1 || (mode < 0 && p.cols <= kStagedAutoMaxCols)) {
+            const int staged = dispatch_rows_staged<Op>(p, info, stream);
+            if (staged != FDL_ERR_UNSUPPORTED || mode == 1) return staged;
+        }
         FDL_ROW_DISPATCH(launch_direct_cfg);
     }
     int64_t grid = p.rows;

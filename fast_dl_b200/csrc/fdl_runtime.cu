@@ -172,7 +172,7 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().cols_ctas_per_sm = value;
         return FDL_OK;
     }
-    if (k == "rows_staged" && (value == 0 || value == 1)) {
+    if (k == "rows_staged" && value >= -1 && value <= 1) {
         fdl::tuning().rows_staged = value;
         return FDL_OK;
     }

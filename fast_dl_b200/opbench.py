@@ -158,7 +158,7 @@ def main(ref=None) -> None:
                    (lambda op=op: ref.gpu_activation(L.data_ptr(), out.data_ptr(), R * C, op)) if ref else None)
 
     if "rows" in cfgs:  # extra row-wise shapes: short and long rows
-        for R, C in ((1 << 20, 64), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384)):
+        for R, C in ((1 << 21, 32), (1 << 20, 64), (1 << 19, 128), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384)):
             L = normal((R, C), 3.0)
             out = torch.empty_like(L)
             record("row", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
