@@ -465,6 +465,7 @@ struct SumRed {
     __device__ static State lift(float v, int) { return v; }
     __device__ static State combine(State a, State b) { return a + b; }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    __device__ static State load_cg(const State* p) { return __ldcg(p); }  // L2, never a stale L1 line
     __device__ static Out finish(State a, int64_t, float) { return a; }
 };
 struct MeanRed : SumRed {
@@ -478,6 +479,7 @@ struct MaxRed {
     __device__ static State lift(float v, int) { return v; }
     __device__ static State combine(State a, State b) { return fmaxf(a, b); }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    __device__ static State load_cg(const State* p) { return __ldcg(p); }
     __device__ static Out finish(State a, int64_t, float) { return a; }
 };
 struct ArgState {
@@ -499,6 +501,7 @@ struct ArgmaxRed {
     __device__ static State shuffle_xor(State a, int o) {
         return ArgState{__shfl_xor_sync(kFullMask, a.v, o), __shfl_xor_sync(kFullMask, a.i, o)};
     }
+    __device__ static State load_cg(const State* p) { return ArgState{__ldcg(&p->v), __ldcg(&p->i)}; }
     __device__ static Out finish(State a, int64_t, float) {
         return a.i == INT_MAX ? 0 : static_cast<int64_t>(a.i);
     }
@@ -506,6 +509,90 @@ struct ArgmaxRed {
 
 constexpr int kRowThreads = 256;
 constexpr int kRowUnroll = 4;  // independent accumulator chains per thread
+
+// What one thread makes of the items first, first + STRIDE, ... < npack of a row (items are
+// 128-bit packs when W = 4, floats when W = 1): kRowUnroll independent chains, combined.
+template <class R, int W, int STRIDE>
+__device__ __forceinline__ typename R::State thread_reduce_span(const float* xr, int first, int npack) {
+    using State = typename R::State;
+    State acc[kRowUnroll];
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
+    int p = first;
+    if (R::kIsArgmax && W == 4) {
+        // Argmax works on whole packs: three fmaxf (which skip NaNs) and one compare per
+        // 128-bit load.  Only when a pack beats the running maximum -- rare once a few
+        // packs have been seen -- is the winning lane inside it worked out.
+        const float4* xv = reinterpret_cast<const float4*>(xr);
+        float best[kRowUnroll];
+        int best_col[kRowUnroll];
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) {
+            best[u] = -INFINITY;
+            best_col[u] = INT_MAX;
+        }
+        for (; p + (kRowUnroll - 1) * STRIDE < npack; p += kRowUnroll * STRIDE) {
+            float4 v[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * STRIDE);
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                const float m4 = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
+                if (m4 > best[u]) {
+                    best[u] = m4;
+                    best_col[u] = (p + u * STRIDE) * 4 +
+                                  (v[u].x == m4 ? 0 : (v[u].y == m4 ? 1 : (v[u].z == m4 ? 2 : 3)));
+                }
+            }
+        }
+        for (; p < npack; p += STRIDE) {
+            const float4 v = ld_stream(xv + p);
+            const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            if (m4 > best[0]) {
+                best[0] = m4;
+                best_col[0] = p * 4 + (v.x == m4 ? 0 : (v.y == m4 ? 1 : (v.z == m4 ? 2 : 3)));
+            }
+        }
+        // Chains hold disjoint, interleaved column sets: ties go to the lower column.
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::lift(best[u], best_col[u]);
+    } else if (W == 4) {
+        const float4* xv = reinterpret_cast<const float4*>(xr);
+        for (; p + (kRowUnroll - 1) * STRIDE < npack; p += kRowUnroll * STRIDE) {
+            float4 v[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * STRIDE);
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                const int c = (p + u * STRIDE) * 4;
+                acc[u] = R::combine(acc[u], R::lift(v[u].x, c));
+                acc[u] = R::combine(acc[u], R::lift(v[u].y, c + 1));
+                acc[u] = R::combine(acc[u], R::lift(v[u].z, c + 2));
+                acc[u] = R::combine(acc[u], R::lift(v[u].w, c + 3));
+            }
+        }
+        for (; p < npack; p += STRIDE) {
+            const float4 v = ld_stream(xv + p);
+            const int c = p * 4;
+            acc[0] = R::combine(acc[0], R::lift(v.x, c));
+            acc[0] = R::combine(acc[0], R::lift(v.y, c + 1));
+            acc[0] = R::combine(acc[0], R::lift(v.z, c + 2));
+            acc[0] = R::combine(acc[0], R::lift(v.w, c + 3));
+        }
+    } else {
+        for (; p + (kRowUnroll - 1) * STRIDE < npack; p += kRowUnroll * STRIDE) {
+            float v[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xr + p + u * STRIDE);
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                acc[u] = R::combine(acc[u], R::lift(v[u], p + u * STRIDE));
+            }
+        }
+        for (; p < npack; p += STRIDE) acc[0] = R::combine(acc[0], R::lift(ld_stream(xr + p), p));
+    }
+    return R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+}
 
 // TPR threads cooperate on a row (32: one warp per row, 8 rows per CTA; 256: one CTA per
 // row).  W = 4 needs cols % 4 == 0 and a 16-byte aligned base.
@@ -523,84 +610,7 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
 
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + team; row < rows;
          row += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
-        const float* xr = x + row * cols;
-        State acc[kRowUnroll];
-#pragma unroll
-        for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
-        int p = t;
-        if (R::kIsArgmax && W == 4) {
-            // Argmax works on whole packs: three fmaxf (which skip NaNs) and one compare per
-            // 128-bit load.  Only when a pack beats the running maximum -- rare once a few
-            // packs have been seen -- is the winning lane inside it worked out.
-            const float4* xv = reinterpret_cast<const float4*>(xr);
-            float best[kRowUnroll];
-            int best_col[kRowUnroll];
-#pragma unroll
-            for (int u = 0; u < kRowUnroll; ++u) {
-                best[u] = -INFINITY;
-                best_col[u] = INT_MAX;
-            }
-            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
-                float4 v[kRowUnroll];
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * TPR);
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) {
-                    const float m4 = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
-                    if (m4 > best[u]) {
-                        best[u] = m4;
-                        best_col[u] = (p + u * TPR) * 4 +
-                                      (v[u].x == m4 ? 0 : (v[u].y == m4 ? 1 : (v[u].z == m4 ? 2 : 3)));
-                    }
-                }
-            }
-            for (; p < npack; p += TPR) {
-                const float4 v = ld_stream(xv + p);
-                const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-                if (m4 > best[0]) {
-                    best[0] = m4;
-                    best_col[0] = p * 4 + (v.x == m4 ? 0 : (v.y == m4 ? 1 : (v.z == m4 ? 2 : 3)));
-                }
-            }
-            // Chains hold disjoint, interleaved column sets: ties go to the lower column.
-#pragma unroll
-            for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::lift(best[u], best_col[u]);
-        } else if (W == 4) {
-            const float4* xv = reinterpret_cast<const float4*>(xr);
-            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
-                float4 v[kRowUnroll];
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xv + p + u * TPR);
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) {
-                    const int c = (p + u * TPR) * 4;
-                    acc[u] = R::combine(acc[u], R::lift(v[u].x, c));
-                    acc[u] = R::combine(acc[u], R::lift(v[u].y, c + 1));
-                    acc[u] = R::combine(acc[u], R::lift(v[u].z, c + 2));
-                    acc[u] = R::combine(acc[u], R::lift(v[u].w, c + 3));
-                }
-            }
-            for (; p < npack; p += TPR) {
-                const float4 v = ld_stream(xv + p);
-                const int c = p * 4;
-                acc[0] = R::combine(acc[0], R::lift(v.x, c));
-                acc[0] = R::combine(acc[0], R::lift(v.y, c + 1));
-                acc[0] = R::combine(acc[0], R::lift(v.z, c + 2));
-                acc[0] = R::combine(acc[0], R::lift(v.w, c + 3));
-            }
-        } else {
-            for (; p + (kRowUnroll - 1) * TPR < npack; p += kRowUnroll * TPR) {
-                float v[kRowUnroll];
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) v[u] = ld_stream(xr + p + u * TPR);
-#pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) {
-                    acc[u] = R::combine(acc[u], R::lift(v[u], p + u * TPR));
-                }
-            }
-            for (; p < npack; p += TPR) acc[0] = R::combine(acc[0], R::lift(ld_stream(xr + p), p));
-        }
-        State s = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+        State s = thread_reduce_span<R, W, TPR>(x + row * cols, t, npack);
 #pragma unroll
         for (int o = kWarp / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
         if (TPR == kWarp) {
@@ -618,6 +628,243 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
             __syncthreads();
         }
     }
+}
+
+// Short rows (up to 64 items: packs when W = 4, floats when W = 1).  A team of TPR lanes
+// (a power of two) owns a row, every lane holds L items of it, and each team keeps U rows in
+// flight, so a thread has L * U loads outstanding however short the row is.  Teams take
+// consecutive rows, so a warp's loads are contiguous when TPR equals the row's item count.
+template <class R, int TPR, int L, int U, int W>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_rows_narrow_kernel(const float* x, int64_t rows, int cols, typename R::Out* out, float divisor) {
+    using State = typename R::State;
+    constexpr int kTeams = kRowThreads / TPR;
+    const int t = threadIdx.x % TPR;
+    const int team = threadIdx.x / TPR;
+    const int nitem = cols / W;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * (kTeams * U) + team;
+
+    float v[U][L][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        const float* xr = x + row * cols;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            const int item = t + l * TPR;
+            if (row < rows && item < nitem) {
+                if (W == 4) {
+                    const float4 q = ld_stream(reinterpret_cast<const float4*>(xr) + item);
+                    v[u][l][0] = q.x; v[u][l][1 % W] = q.y; v[u][l][2 % W] = q.z; v[u][l][3 % W] = q.w;
+                } else {
+                    v[u][l][0] = ld_stream(xr + item);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        State s = R::identity();
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            const int item = t + l * TPR;
+            if (row < rows && item < nitem) {
+#pragma unroll
+                for (int k = 0; k < W; ++k) s = R::combine(s, R::lift(v[u][l][k], item * W + k));
+            }
+        }
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
+        if (t == 0 && row < rows) out[row] = R::finish(s, cols, divisor);
+    }
+}
+
+// Argmax of short rows.  The generic state (value, column) costs two shuffles and a
+// three-way select per step; here only the row maximum travels through the shuffles and one
+// ballot per item slot finds the lowest lane that holds it.  Items are visited slot-major
+// (slot 0 of every lane precedes slot 1 of any lane, as the columns do), so ties go to the
+// lowest column; NaN ranks as -inf, and a row whose maximum is -inf answers column 0.
+template <int TPR, int L, int U, int W>
+__global__ void __launch_bounds__(kRowThreads)
+argmax_rows_narrow_kernel(const float* x, int64_t rows, int cols, int64_t* out, float) {
+    constexpr int kTeams = kRowThreads / TPR;
+    const int t = threadIdx.x % TPR;
+    const int team = threadIdx.x / TPR;
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int team_shift = lane - t;  // first lane of this team inside its warp
+    const unsigned int team_mask = TPR == kWarp ? kFullMask : ((1u << TPR) - 1u);
+    const int nitem = cols / W;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * (kTeams * U) + team;
+
+    float v[U][L][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        const float* xr = x + row * cols;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            const int item = t + l * TPR;
+            if (row < rows && item < nitem) {
+                if (W == 4) {
+                    const float4 q = ld_stream(reinterpret_cast<const float4*>(xr) + item);
+                    v[u][l][0] = q.x; v[u][l][1 % W] = q.y; v[u][l][2 % W] = q.z; v[u][l][3 % W] = q.w;
+                } else {
+                    v[u][l][0] = ld_stream(xr + item);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < W; ++k) v[u][l][k] = -INFINITY;
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        float m[L];
+        float best = -INFINITY;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            float q = v[u][l][0];
+            if (W == 4) q = fmaxf(fmaxf(q, v[u][l][1 % W]), fmaxf(v[u][l][2 % W], v[u][l][3 % W]));
+            m[l] = fmaxf(q, -INFINITY);  // fmaxf skips NaNs; an all-NaN item becomes -inf
+            best = fmaxf(best, m[l]);
+        }
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(kFullMask, best, o));
+        bool found = false;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            const unsigned int votes = (__ballot_sync(kFullMask, m[l] == best) >> team_shift) & team_mask;
+            if (!found && votes != 0u) {
+                found = true;
+                if (t == __ffs(static_cast<int>(votes)) - 1 && row < rows) {
+                    int col = (t + l * TPR) * W;
+                    if (W == 4) {
+                        col += v[u][l][0] == best ? 0 : (v[u][l][1 % W] == best ? 1 : (v[u][l][2 % W] == best ? 2 : 3));
+                    }
+                    out[row] = best == -INFINITY ? 0 : static_cast<int64_t>(col);
+                }
+            }
+        }
+    }
+}
+
+template <class R, int TPR, int L, int U, int W>
+struct NarrowKernel {
+    static constexpr auto fn = reduce_rows_narrow_kernel<R, TPR, L, U, W>;
+};
+template <int TPR, int L, int U, int W>
+struct NarrowKernel<ArgmaxRed, TPR, L, U, W> {
+    static constexpr auto fn = argmax_rows_narrow_kernel<TPR, L, U, W>;
+};
+
+template <class R, int TPR, int L, int U, int W>
+int launch_rows_narrow_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
+                           cudaStream_t stream) {
+    constexpr int kRowsPerCta = kRowThreads / TPR * U;
+    const int64_t grid = ceil_div(rows, kRowsPerCta);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    NarrowKernel<R, TPR, L, U, W>::fn<<<static_cast<unsigned int>(grid), kRowThreads, 0, stream>>>(
+        x, rows, static_cast<int>(cols), out, static_cast<float>(cols));
+    return launch_status();
+}
+
+constexpr int kNarrowMaxItems = 64;
+
+template <class R, int W>
+int launch_rows_narrow(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
+                       cudaStream_t stream) {
+    const int64_t nitem = cols / W;
+    if (nitem <= 1) return launch_rows_narrow_cfg<R, 1, 1, 8, W>(x, rows, cols, out, stream);
+    if (nitem <= 2) return launch_rows_narrow_cfg<R, 2, 1, 8, W>(x, rows, cols, out, stream);
+    if (nitem <= 4) return launch_rows_narrow_cfg<R, 4, 1, 8, W>(x, rows, cols, out, stream);
+    if (nitem <= 8) return launch_rows_narrow_cfg<R, 8, 1, 8, W>(x, rows, cols, out, stream);
+    if (nitem <= 16) return launch_rows_narrow_cfg<R, 16, 1, 8, W>(x, rows, cols, out, stream);
+    if (nitem <= 32) return launch_rows_narrow_cfg<R, 32, 1, 8, W>(x, rows, cols, out, stream);
+    return launch_rows_narrow_cfg<R, 32, 2, 4, W>(x, rows, cols, out, stream);
+}
+
+// A few very long rows: one CTA per row would leave most SMs idle, so every row is cut into
+// segments of about 64 KiB, one CTA each (grid = segments x rows).  A CTA leaves its
+// segment's state in scratch; the last CTA of a row to arrive (ticket counter) folds the
+// row's segment states -- thread k takes segments k, k + 256, ... in order, then the usual
+// tree -- so the result does not depend on which CTA came last.  Sums, maxima and argmax
+// (ties: lowest column) all go through the same State type.
+template <class R, int W>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_rows_split_kernel(const float* x, int cols, int seg_items, typename R::State* partials,
+                         unsigned int* counters, typename R::Out* out, float divisor) {
+    using State = typename R::State;
+    __shared__ State red[kRowThreads / kWarp];
+    __shared__ bool is_last;
+    const int lane = threadIdx.x & (kWarp - 1);
+    const int warp = threadIdx.x / kWarp;
+    const int64_t row = blockIdx.y;
+    const int nseg = gridDim.x;
+    const int seg = blockIdx.x;
+    const int nitem = cols / W;
+    const int begin = seg * seg_items;
+    int end = begin + seg_items;
+    if (end > nitem) end = nitem;
+
+    State s = thread_reduce_span<R, W, kRowThreads>(x + row * cols, begin + static_cast<int>(threadIdx.x), end);
+    auto cta_fold = [&](State z) {
+#pragma unroll
+        for (int o = kWarp / 2; o > 0; o >>= 1) z = R::combine(z, R::shuffle_xor(z, o));
+        if (lane == 0) red[warp] = z;
+        __syncthreads();
+        z = lane < kRowThreads / kWarp ? red[lane] : R::identity();
+#pragma unroll
+        for (int o = kWarp / 2; o > 0; o >>= 1) z = R::combine(z, R::shuffle_xor(z, o));
+        __syncthreads();
+        return z;  // every thread of warp 0 holds the CTA's state
+    };
+    s = cta_fold(s);
+    if (threadIdx.x == 0) {
+        partials[row * nseg + seg] = s;
+        __threadfence();
+        const unsigned int ticket = atomicAdd(counters + row, 1u);
+        is_last = ticket == static_cast<unsigned int>(nseg - 1);
+        if (is_last) counters[row] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    State z = R::identity();
+    const State* mine = partials + row * nseg;
+    for (int k = threadIdx.x; k < nseg; k += kRowThreads) z = R::combine(z, R::load_cg(mine + k));
+    z = cta_fold(z);
+    if (threadIdx.x == 0) out[row] = R::finish(z, cols, divisor);
+}
+
+constexpr int64_t kSplitMaxRows = 1184;               // below 8 CTAs per SM of a B200
+constexpr int64_t kSplitMinRowBytes = 256 * 1024;     // and rows long enough to cut
+constexpr int64_t kSplitSegmentBytes = 64 * 1024;
+constexpr int kSplitMaxSegments = 1024;
+
+template <class R, int W>
+int launch_rows_split(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
+                      cudaStream_t stream) {
+    using State = typename R::State;
+    const int64_t nitem = cols / W;
+    int64_t nseg = ceil_div(cols * 4, kSplitSegmentBytes);
+    if (nseg > kSplitMaxSegments) nseg = kSplitMaxSegments;
+    // whole 128-byte lines per segment, so that segments of a row do not share a line
+    const int64_t line_items = 128 / (4 * W);
+    const int64_t seg_items = ceil_div(ceil_div(nitem, nseg), line_items) * line_items;
+    nseg = ceil_div(nitem, seg_items);
+    void* scratch = nullptr;
+    const size_t need = kCounterBytes + static_cast<size_t>(rows) * nseg * sizeof(State);
+    const int status = get_workspace(need, &scratch);
+    if (status != FDL_OK) return status;
+    unsigned int* counters = static_cast<unsigned int*>(scratch);
+    State* partials = reinterpret_cast<State*>(static_cast<char*>(scratch) + kCounterBytes);
+    const dim3 grid(static_cast<unsigned int>(nseg), static_cast<unsigned int>(rows));
+    reduce_rows_split_kernel<R, W><<<grid, kRowThreads, 0, stream>>>(
+        x, static_cast<int>(cols), static_cast<int>(seg_items), partials, counters, out,
+        static_cast<float>(cols));
+    return launch_status();
 }
 
 template <class R, int TPR, int W>
@@ -640,6 +887,14 @@ int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out
     if (x == nullptr || out == nullptr || cols == 0) return FDL_ERR_INVALID_ARGUMENT;
     if (cols >= INT_MAX) return FDL_ERR_UNSUPPORTED;
     const bool vec = aligned16(x) && cols % 4 == 0;
+    if ((vec ? cols / 4 : cols) <= kNarrowMaxItems) {
+        return vec ? launch_rows_narrow<R, 4>(x, rows, cols, out, stream)
+                   : launch_rows_narrow<R, 1>(x, rows, cols, out, stream);
+    }
+    if (rows < kSplitMaxRows && cols * 4 >= kSplitMinRowBytes) {
+        return vec ? launch_rows_split<R, 4>(x, rows, cols, out, stream)
+                   : launch_rows_split<R, 1>(x, rows, cols, out, stream);
+    }
     const bool wide = cols >= 2048;  // a whole CTA per row once a warp would loop too long
     if (vec) {
         return wide ? launch_rows_cfg<R, kRowThreads, 4>(x, rows, cols, out, stream)
@@ -838,7 +1093,10 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     g->w = vec ? 4 : 1;
     const int64_t packs = ceil_div(cols, g->w);
     int tx = 1;
-    const int tx_max = tuning().cols_tx;  // threads across columns (x4 floats = row bytes per CTA)
+    int tx_max = tuning().cols_tx;  // threads across columns (x4 floats = row bytes per CTA)
+    // With few rows, thread rows beyond rows / 8 would sit idle: widen the tile instead (a
+    // matrix of three rows is walked like an elementwise op, one thread per pack of columns).
+    while (tx_max < kColThreads && static_cast<int64_t>(kColThreads / tx_max) * 8 > rows) tx_max <<= 1;
     while (tx < tx_max && tx < packs) tx <<= 1;
     g->tx = tx;
     g->col_blocks = static_cast<int>(ceil_div(packs, tx));
@@ -862,9 +1120,18 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
         g->cluster = want_cluster;
         g->chunks = static_cast<int>(ceil_div(g->chunks, want_cluster)) * want_cluster;
     }
-    const int groups = g->chunks / g->cluster;
+    int groups = g->chunks / g->cluster;
     const size_t ncounters = static_cast<size_t>(g->col_blocks) * batch;
-    if (ncounters * sizeof(unsigned int) > static_cast<size_t>(kCounterBytes)) return FDL_ERR_UNSUPPORTED;
+    if (groups > 1 && ncounters * sizeof(unsigned int) > static_cast<size_t>(kCounterBytes)) {
+        // More column blocks than arrival counters: such a matrix is wide enough to fill the
+        // GPU with one CTA per column block, each walking all the rows, and needs neither
+        // partials nor counters.
+        g->rows_per_chunk = static_cast<int>(rows < 2147483647 ? rows : 2147483647);
+        if (g->rows_per_chunk != rows) return FDL_ERR_UNSUPPORTED;
+        g->chunks = 1;
+        g->cluster = 1;
+        groups = 1;
+    }
     g->counter_bytes = kCounterBytes;
     g->scratch_bytes =
         groups == 1

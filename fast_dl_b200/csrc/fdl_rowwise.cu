@@ -20,7 +20,10 @@
 // 97-98%, so the default picks by row length.  Both forms stay selectable so the
 // comparison can be repeated on the same build.
 //
-// Rows that are unaligned, not a multiple of 4 floats, or longer than 16384 floats take a
+// Rows of 16384 < cols <= 131072 floats are shared by a thread-block cluster of 2, 4 or 8
+// CTAs: each keeps a slice in registers and the row statistics cross the cluster through
+// distributed shared memory, so such a row is still read once and written once.
+// Rows that are unaligned, not a multiple of 4 floats, or longer than that take a
 // plain three-pass kernel (second and third pass hit L2).
 //
 // The one mbarrier wait is bounded; if it runs out the CTA raises a flag in host-visible
@@ -29,9 +32,13 @@
 #include <cmath>
 #include <type_traits>
 
+#include <cooperative_groups.h>
+
 #include "fdl_common.cuh"
 
 namespace fdl {
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -96,20 +103,56 @@ __device__ __forceinline__ float team_sum(float v, float* red) {
     return r;
 }
 
+// Where a row's statistics are folded: inside a team of one CTA ...
+template <int TPR, int TH>
+struct TeamScope {
+    float* red;
+    __device__ __forceinline__ float max(float v) { return team_max<TPR, TH>(v, red); }
+    __device__ __forceinline__ float sum(float v) { return team_sum<TPR, TH>(v, red); }
+};
+
+// ... or across the CTAs of a thread-block cluster that share one long row.  Every CTA folds
+// its slice, thread 0 drops the value into slot [phase][rank] of EVERY CTA's shared memory
+// (distributed shared memory), and after a cluster barrier each CTA adds the CL slots in rank
+// order, so all of them continue with the same bits.
+template <int CL, int TH>
+struct ClusterScope {
+    float* red;
+    float (*slots)[8];  // [2 phases][up to 8 ranks], in every CTA of the cluster
+    int phase;
+    __device__ __forceinline__ float exchange(float cta_value, bool is_max) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (threadIdx.x == 0) {
+            const unsigned int me = cluster.block_rank();
+#pragma unroll
+            for (int k = 0; k < CL; ++k) cluster.map_shared_rank(&slots[0][0], k)[phase * 8 + me] = cta_value;
+        }
+        cluster.sync();
+        float r = slots[phase][0];
+#pragma unroll
+        for (int k = 1; k < CL; ++k) r = is_max ? fmaxf(r, slots[phase][k]) : r + slots[phase][k];
+        phase ^= 1;
+        return r;
+    }
+    __device__ __forceinline__ float max(float v) { return exchange(team_max<TH, TH>(v, red), true); }
+    __device__ __forceinline__ float sum(float v) { return exchange(team_sum<TH, TH>(v, red), false); }
+};
+
 // ---- per-row arithmetic on a register-resident row -----------------------------------------
 //
 // `active` is false for the lanes of a team that has no row (past the end); they run the
 // same shuffles on neutral values and store nothing.
 
-template <int TPR, int TH, int NV>
+template <int TPR, int TH, int NV, class Scope>
 __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int nvec,
-                                         const RowParams& p, int64_t row, bool active, float* red) {
+                                         const RowParams& p, int64_t row, bool active, Scope& scope,
+                                         int voff = 0) {
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     }
-    m = team_max<TPR, TH>(m, red);
+    m = scope.max(m);
     // exp(x - m) as 2^((x - m) * log2(e)): the subtraction is the reference's own (exact
     // for the terms that matter, by Sterbenz), then one multiply and one ex2.approx
     // (relative error ~2^-22) instead of the ~9-instruction expf.
@@ -125,10 +168,10 @@ __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int 
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     }
-    s = team_sum<TPR, TH>(s, red);
+    s = scope.sum(s);
     if (!active) return;
     const float norm = 1.0f / s;
-    float4* yr = reinterpret_cast<float4*>(p.y + row * p.cols);
+    float4* yr = reinterpret_cast<float4*>(p.y + row * p.cols) + voff;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) {
@@ -138,16 +181,17 @@ __device__ __forceinline__ void row_math(SoftmaxOp, float4 (&v)[NV], int t, int 
     }
 }
 
-template <int TPR, int TH, int NV>
+template <int TPR, int TH, int NV, class Scope>
 __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, int nvec,
-                                         const RowParams& p, int64_t row, bool active, float* red) {
+                                         const RowParams& p, int64_t row, bool active, Scope& scope,
+                                         int voff = 0) {
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
     const float inv_n = 1.0f / static_cast<float>(p.cols);
-    const float mean = team_sum<TPR, TH>(s, red) * inv_n;
+    const float mean = scope.sum(s) * inv_n;
     // Second moment about the mean from the registers: no E[x^2] - E[x]^2 cancellation.
     float q = 0.0f;
 #pragma unroll
@@ -158,16 +202,16 @@ __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, in
             q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
         }
     }
-    const float var = team_sum<TPR, TH>(q, red) * inv_n;
+    const float var = scope.sum(q) * inv_n;
     if (!active) return;
     const float rstd = 1.0f / sqrtf(var + p.eps);
-    if (t == 0) {
+    if (t == 0 && voff == 0) {
         if (p.mean_out != nullptr) p.mean_out[row] = mean;
         if (p.rstd_out != nullptr) p.rstd_out[row] = rstd;
     }
-    float4* yr = reinterpret_cast<float4*>(p.y + row * p.cols);
-    const float4* g4 = reinterpret_cast<const float4*>(p.gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(p.beta);
+    float4* yr = reinterpret_cast<float4*>(p.y + row * p.cols) + voff;
+    const float4* g4 = p.gamma == nullptr ? nullptr : reinterpret_cast<const float4*>(p.gamma) + voff;
+    const float4* b4 = p.beta == nullptr ? nullptr : reinterpret_cast<const float4*>(p.beta) + voff;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = t + i * TPR;
@@ -214,10 +258,71 @@ rows_direct_kernel(const RowParams p) {
             v[i] = active ? ld_stream(src + t + i * TPR) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, row, active, red);
+    TeamScope<TPR, TH> scope{red};
+    row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, row, active, scope);
 }
 
 // ---- staged form: one bulk copy per CTA ---------------------------------------------------------
+
+// ---- cluster form: rows of 16384 < cols <= 8 x 16384 floats -----------------------------------------
+//
+// A thread-block cluster of CL CTAs (512 threads, 8 packs each) owns one row: CTA `rank`
+// keeps slice `rank` of it in registers, the row statistics cross the cluster through
+// distributed shared memory (ClusterScope), and the row is still read once and written once.
+
+constexpr int kClusterThreads = 512;
+constexpr int kClusterNV = 8;
+
+template <class Op, int CL>
+__global__ void __launch_bounds__(kClusterThreads, 2)
+rows_cluster_kernel(const RowParams p, int slice_vecs) {
+    __shared__ float red[kMaxWarps];
+    __shared__ float slots[2][8];
+    cg::cluster_group cluster = cg::this_cluster();
+    // Every CTA of the cluster must be running before anyone stores into its shared memory:
+    // arrive now, wait after the loads have been issued.
+    cluster.barrier_arrive();
+    const int64_t row = blockIdx.x / CL;
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int nvec = p.cols / 4;
+    const int voff = rank * slice_vecs;
+    int local = nvec - voff;
+    if (local > slice_vecs) local = slice_vecs;
+    if (local < 0) local = 0;
+    const int t = threadIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols) + voff;
+    float4 v[kClusterNV];
+#pragma unroll
+    for (int i = 0; i < kClusterNV; ++i) {
+        if (t + i * kClusterThreads < local) v[i] = ld_stream(src + t + i * kClusterThreads);
+    }
+    cluster.barrier_wait();
+    ClusterScope<CL, kClusterThreads> scope{red, slots, 0};
+    row_math<kClusterThreads, kClusterThreads, kClusterNV>(Op{}, v, t, local, p, row, true, scope, voff);
+}
+
+template <class Op, int CL>
+int launch_cluster_cfg(const RowParams& p, cudaStream_t stream) {
+    const int nvec = p.cols / 4;
+    const int slice_vecs = static_cast<int>(ceil_div(static_cast<int64_t>(nvec), CL));
+    if (p.rows * CL > 2147483647) return FDL_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned int>(p.rows * CL));
+    cfg.blockDim = dim3(kClusterThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CL;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, rows_cluster_kernel<Op, CL>, p, slice_vecs);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_status();
+}
+
+// ---- staged form -------------------------------------------------------------------------------
 
 template <class Op, int TPR, int TH, int NV>
 __global__ void __launch_bounds__(TH, min_ctas_for(TH, NV))
@@ -263,7 +368,8 @@ rows_staged_kernel(const RowParams p) {
                 v[i] = active ? src[r * nvec + t + i * TPR] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, r0 + r, active, red);
+        TeamScope<TPR, TH> scope{red};
+        row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, r0 + r, active, scope);
     }
 }
 
@@ -392,9 +498,16 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     status = error_flag_device_ptr(&p.error_flag);
     if (status != FDL_OK) return status;
 
-    const bool in_registers = p.cols % 4 == 0 && p.cols <= 16384 && aligned16(p.x) &&
-                              aligned16(p.y) && (p.gamma == nullptr || aligned16(p.gamma)) &&
-                              (p.beta == nullptr || aligned16(p.beta));
+    const bool packs = p.cols % 4 == 0 && aligned16(p.x) && aligned16(p.y) &&
+                       (p.gamma == nullptr || aligned16(p.gamma)) &&
+                       (p.beta == nullptr || aligned16(p.beta));
+    constexpr int kCtaMaxCols = kClusterThreads * kClusterNV * 4;  // 16384 floats in one CTA's registers
+    if (packs && p.cols > kCtaMaxCols && p.cols <= 8 * kCtaMaxCols) {
+        if (p.cols <= 2 * kCtaMaxCols) return launch_cluster_cfg<Op, 2>(p, stream);
+        if (p.cols <= 4 * kCtaMaxCols) return launch_cluster_cfg<Op, 4>(p, stream);
+        return launch_cluster_cfg<Op, 8>(p, stream);
+    }
+    const bool in_registers = packs && p.cols <= kCtaMaxCols;
     if (in_registers) {
         // -1 (default): staged for rows of up to 128 floats, where a thread of the direct
         // form has a single load in flight (measured 97-98% of the copy bandwidth staged

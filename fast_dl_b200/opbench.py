@@ -158,12 +158,44 @@ def main(ref=None) -> None:
                    (lambda op=op: ref.gpu_activation(L.data_ptr(), out.data_ptr(), R * C, op)) if ref else None)
 
     if "rows" in cfgs:  # extra row-wise shapes: short and long rows
-        for R, C in ((1 << 21, 32), (1 << 20, 64), (1 << 19, 128), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384)):
+        for R, C in ((1 << 21, 32), (1 << 20, 64), (1 << 19, 128), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384),
+                     (2048, 32768), (1024, 65536), (512, 131072), (128, 524288)):
             L = normal((R, C), 3.0)
             out = torch.empty_like(L)
             record("row", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
             record("row", f"layernorm [{R},{C}]", 8 * R * C, lambda: capi.layernorm_rows(L, out=out))
             del L, out
+
+    if "shapes" in cfgs:  # 256 MiB inputs in shapes far from the configurations': where are the weak spots?
+        n = 1 << 26
+        for R, C in ((1 << 21, 32), (1 << 19, 128), (1 << 17, 512), (1 << 13, 8192), (64, 1 << 20), (3, n // 12 * 4)):
+            X = normal((R, C))
+            record("shp", f"sum axis 1 [{R},{C}]", 4 * R * C + 4 * R, lambda: capi.reduce_rows(X, capi.REDUCE_SUM))
+            record("shp", f"argmax axis 1 [{R},{C}]", 4 * R * C + 8 * R, lambda: capi.argmax_rows(X))
+            record("shp", f"mean axis 0 [{R},{C}]", 4 * R * C + 4 * C, lambda: capi.reduce_cols(X, capi.REDUCE_MEAN))
+            del X
+        X = normal((64, 1024, 1024))
+        record("shp", "mean axis 1 of [64,1024,1024] (batched)", 4 * n + 4 * 65536,
+               lambda: capi.reduce_cols(X, capi.REDUCE_MEAN))
+        out = torch.empty_like(X)
+        for name, other in (("[64,1024,1024] + [1024] (innermost)", uniform((1024,))),
+                            ("[64,1024,1024] + [1024,1] (middle)", uniform((1024, 1))),
+                            ("[64,1024,1024] + [64,1,1] (outermost)", uniform((64, 1, 1))),
+                            ("[64,1024,1024] + [64,1,1024]", uniform((64, 1, 1024))),
+                            ("[64,1024,1024] + [1,1024,1]", uniform((1, 1024, 1)))):
+            record("shp", name, 8 * n + 4 * other.numel(),
+                   lambda other=other: capi.broadcast_binary(X, other, capi.ADD, out=out))
+        X4 = X.view(64, 64, 128, 128)
+        out4 = out.view(64, 64, 128, 128)
+        ch = uniform((1, 64, 1, 1))
+        record("shp", "[64,64,128,128] * [1,64,1,1] (per channel)", 8 * n + 256,
+               lambda: capi.broadcast_binary(X4, ch, capi.MUL, out=out4))
+        flat, oflat = X.view(-1), out.view(-1)
+        record("shp", "add, operands offset by 4 bytes (scalar path)", 12 * (n - 1),
+               lambda: capi.binary(flat[1:], out.view(-1)[1:], capi.ADD, out=oflat[1:]))
+        for k in (1 << 10, 1 << 14, 1 << 18, 1 << 22):
+            record("shp", f"full sum of {k} elements", 4 * k + 4, lambda k=k: capi.full_sum(flat[:k]))
+        del X, out
 
     if "c5" in cfgs:
         n, C = 1 << 28, 16384

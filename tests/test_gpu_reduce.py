@@ -70,9 +70,13 @@ def test_full_sum_is_deterministic_and_scratch_is_reusable(fdl, cuda):
 
 SHAPES = [(1, 1), (1, 7), (5, 3), (17, 128), (33, 1000), (64, 2048), (9, 2052), (300, 4096), (3, 100003),
           (2048, 33), (1024, 1024)]
+# short rows (teams of 1..32 lanes, several rows in flight) and a few very long rows (cut into segments)
+ROW_SHAPES = SHAPES + [(100000, 4), (70001, 8), (50000, 12), (33333, 32), (20000, 36), (9999, 64), (5000, 128),
+                       (4097, 200), (3000, 256), (3001, 260), (1000, 2), (777, 37), (500, 64), (501, 65),
+                       (3, 1 << 20), (5, (1 << 20) + 4), (2, (1 << 21) + 3), (64, 1 << 17), (1, 70000), (1183, 65536)]
 
 
-@pytest.mark.parametrize("rows,cols", SHAPES)
+@pytest.mark.parametrize("rows,cols", ROW_SHAPES)
 def test_row_reductions(fdl, cuda, rows, cols):
     rng = np.random.default_rng(42)
     x = rng.normal(size=(rows, cols)).astype(np.float32)
@@ -82,6 +86,15 @@ def test_row_reductions(fdl, cuda, rows, cols):
     assert_sum_close(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MEAN)), orc.reduce_rows(x, 1), norm / cols, "row mean")
     assert_bit_exact(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "row max")
     np.testing.assert_array_equal(to_np(fdl.argmax_rows(xd)), orc.argmax_rows(x))
+    if cols > 1:   # unaligned base: the 32-bit paths of the same kernels
+        flat = dev(cuda, np.concatenate([np.zeros(1, np.float32), x.reshape(-1)]))
+        xu = flat[1:].view(rows, cols)
+        assert_sum_close(to_np(fdl.reduce_rows(xu, fdl.REDUCE_SUM)), orc.reduce_rows(x, 0), norm, "row sum, unaligned")
+        np.testing.assert_array_equal(to_np(fdl.argmax_rows(xu)), orc.argmax_rows(x))
+    ties = rng.integers(0, 3, size=(rows, cols)).astype(np.float32)
+    np.testing.assert_array_equal(to_np(fdl.argmax_rows(dev(cuda, ties))), orc.argmax_rows(ties))
+    fdl.full_sum(xd.reshape(-1))   # shares the workspace counters with the segmented row kernel
+    assert_bit_exact(to_np(fdl.reduce_rows(xd, fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "row max again")
 
 
 def test_argmax_ties_nan_inf(fdl, cuda):
@@ -95,12 +108,22 @@ def test_argmax_ties_nan_inf(fdl, cuda):
     got = to_np(fdl.argmax_rows(dev(cuda, x)))
     np.testing.assert_array_equal(got, orc.argmax_rows(x))
     assert got.dtype == np.int64 and got[3] == 0 and got[4] == 0 and got[5] == 100
+    for shape in ((3000, 8), (2000, 32), (1000, 128), (4, 1 << 18)):      # the short-row and segmented kernels
+        y = rng.integers(0, 4, size=shape).astype(np.float32)
+        y[1, :] = np.nan
+        y[2, :] = -np.inf
+        y[3, ::3] = np.nan
+        y[0, shape[1] - 1] = np.inf
+        got = to_np(fdl.argmax_rows(dev(cuda, y)))
+        np.testing.assert_array_equal(got, orc.argmax_rows(y))
+        assert got[1] == 0 and got[2] == 0 and got[0] == shape[1] - 1
+        assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, y), fdl.REDUCE_MAX)), orc.reduce_rows(y, 2), f"max {shape}")
     small = rng.integers(0, 3, size=(1000, 37)).astype(np.float32)
     np.testing.assert_array_equal(to_np(fdl.argmax_rows(dev(cuda, small))), orc.argmax_rows(small))
     assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, x), fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "max with nan")
 
 
-@pytest.mark.parametrize("rows,cols", SHAPES + [(8192, 256), (100000, 4)])
+@pytest.mark.parametrize("rows,cols", SHAPES + [(8192, 256), (100000, 4), (3, 5000000), (2, 4500001), (200000, 32)])
 def test_column_reductions(fdl, cuda, rows, cols):
     rng = np.random.default_rng(42)
     x = rng.normal(size=(rows, cols)).astype(np.float32)
