@@ -56,6 +56,9 @@ Tuning& tuning();
 // Per-device workspace the library owns (allocated on first use, grown on demand,
 // never freed before process exit).  Used when a caller passes scratch == NULL.
 int get_workspace(size_t bytes, void** out);
+// Every user of the workspace keeps its arrival counters in the first 64 KiB (zero between
+// launches) and its partial results behind them.
+constexpr int kWorkspaceCounterBytes = 65536;
 
 // One word of host-mapped pinned memory per process in which kernels raise bits when a
 // bounded device-side wait runs out (bit 0: bulk-copy wait, bit 1: cross-GPU exchange wait).

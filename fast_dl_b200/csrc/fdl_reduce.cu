@@ -151,7 +151,7 @@ constexpr int kSumMaxPartials = 8192;                          // doubles in scr
 // Scratch layout shared by the full sum and the column reductions: a fixed 64 KiB region of
 // arrival counters that every kernel leaves zeroed, then the partials.  The region has the
 // same size for every problem so that one scratch buffer can serve calls of any shape.
-constexpr int kCounterBytes = 65536;
+constexpr int kCounterBytes = kWorkspaceCounterBytes;
 constexpr int kStaticCounterBytes = 256;  // the static-scratch entry point has its own array
 
 // Block-wide sum in double; result valid in thread 0.  `red` holds one slot per warp.
@@ -1055,25 +1055,140 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // The last group to arrive folds all group partials of its columns in group order;
-    // loads are issued eight at a time so their latencies overlap.
+    // The last group to arrive folds all group partials of its columns.  Thread row ry takes
+    // groups ry, ry + TY, ... of its own pack of columns (four loads in flight), the TY
+    // results meet in shared memory and are folded in thread-row order: a fixed order, so
+    // the result does not depend on which group came last, and no thread walks more than
+    // groups / TY partials however many row chunks the matrix was cut into.
+    {
+        float s[W];
+#pragma unroll
+        for (int k = 0; k < W; ++k) s[k] = R::identity();
+        if (col < cols) {
+            const float* src = partials + b * cols + col;
+            const int64_t stride = static_cast<int64_t>(gridDim.z) * cols;
+            int g = ry;
+            for (; g + 3 * ty_count < groups; g += 4 * ty_count) {
+                float v[4][W];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float* q = src + (g + j * ty_count) * stride;
+                    if (W == 4) {
+                        const float4 t = __ldcg(reinterpret_cast<const float4*>(q));
+                        v[j][0] = t.x; v[j][1 % W] = t.y; v[j][2 % W] = t.z; v[j][3 % W] = t.w;
+                    } else {
+                        v[j][0] = __ldcg(q);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                    for (int k = 0; k < W; ++k) s[k] = R::combine(s[k], v[j][k]);
+                }
+            }
+            for (; g < groups; g += ty_count) {
+                const float* q = src + g * stride;
+                if (W == 4) {
+                    const float4 t = __ldcg(reinterpret_cast<const float4*>(q));
+                    s[0] = R::combine(s[0], t.x); s[1 % W] = R::combine(s[1 % W], t.y);
+                    s[2 % W] = R::combine(s[2 % W], t.z); s[3 % W] = R::combine(s[3 % W], t.w);
+                } else {
+                    s[0] = R::combine(s[0], __ldcg(q));
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < W; ++k) tile[ry * tile_w + cx * W + k] = s[k];
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
         if (col0 + c >= cols) continue;
-        const float* src = partials + b * cols + col0 + c;
-        const int64_t stride = static_cast<int64_t>(gridDim.z) * cols;
-        float s = R::identity();
-        int k = 0;
-        for (; k + 8 <= groups; k += 8) {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (k + j) * stride);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s = R::combine(s, v[j]);
-        }
-        for (; k < groups; ++k) s = R::combine(s, __ldcg(src + k * stride));
+        float s = tile[c];
+        for (int y = 1; y < ty_count; ++y) s = R::combine(s, tile[y * tile_w + c]);
         s *= scale;
         if (xc.world > 0) s = exchange_column<R>(xc, col0 + c, s);
         out[b * cols + col0 + c] = s;
+    }
+}
+
+// A handful of rows (an average of a few tensors): no tree at all.  Like an elementwise
+// op, every thread owns U packs of columns, has all ROWS x U loads in flight and writes the
+// result; one tile per CTA.  ROWS is a template parameter so that the row loop unrolls.
+constexpr int kFewRows = 8;
+
+template <class R, int W, int ROWS, int U>
+__global__ void __launch_bounds__(kColThreads)
+reduce_cols_few_kernel(const float* x, int64_t cols, float* out, float scale) {
+    const int64_t npack = cols / W;
+    const float* xb = x + static_cast<int64_t>(blockIdx.z) * ROWS * cols;
+    float* ob = out + static_cast<int64_t>(blockIdx.z) * cols;
+    const int64_t tile = static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    const int64_t base = tile * (kColThreads * U) + threadIdx.x;
+    float v[U][ROWS][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t pk = base + u * kColThreads;
+        if (pk < npack) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                const float* src = xb + r * cols + pk * W;
+                if (W == 4) {
+                    const float4 t = ld_stream(reinterpret_cast<const float4*>(src));
+                    v[u][r][0] = t.x; v[u][r][1 % W] = t.y; v[u][r][2 % W] = t.z; v[u][r][3 % W] = t.w;
+                } else {
+                    v[u][r][0] = ld_stream(src);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t pk = base + u * kColThreads;
+        if (pk >= npack) continue;
+        float acc[W];
+#pragma unroll
+        for (int k = 0; k < W; ++k) acc[k] = R::identity();  // so that a NaN-only column gives what the tree gives
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+            for (int k = 0; k < W; ++k) acc[k] = R::combine(acc[k], v[u][r][k]);
+        }
+        float* dst = ob + pk * W;
+        if (W == 4) {
+            st_stream(reinterpret_cast<float4*>(dst),
+                      make_float4(acc[0] * scale, acc[1 % W] * scale, acc[2 % W] * scale, acc[3 % W] * scale));
+        } else {
+            dst[0] = acc[0] * scale;
+        }
+    }
+}
+
+template <class R, int W, int ROWS>
+int launch_cols_few_rows(const float* x, int64_t batch, int64_t cols, float* out, float scale,
+                         cudaStream_t stream) {
+    constexpr int U = ROWS <= 2 ? 4 : (ROWS <= 4 ? 2 : 1);
+    const int64_t tiles = ceil_div(cols / W, static_cast<int64_t>(kColThreads) * U);
+    // tiles fold into a 2-D grid so that any column count fits
+    const int64_t gx = tiles < 65535 ? tiles : 65535;
+    const int64_t gy = ceil_div(tiles, gx);
+    if (gy > 65535) return FDL_ERR_UNSUPPORTED;
+    const dim3 grid(static_cast<unsigned int>(gx), static_cast<unsigned int>(gy), static_cast<unsigned int>(batch));
+    reduce_cols_few_kernel<R, W, ROWS, U><<<grid, kColThreads, 0, stream>>>(x, cols, out, scale);
+    return launch_status();
+}
+
+template <class R, int W>
+int launch_cols_few(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out, float scale,
+                    cudaStream_t stream) {
+    switch (rows) {
+        case 1: return launch_cols_few_rows<R, W, 1>(x, batch, cols, out, scale, stream);
+        case 2: return launch_cols_few_rows<R, W, 2>(x, batch, cols, out, scale, stream);
+        case 3: return launch_cols_few_rows<R, W, 3>(x, batch, cols, out, scale, stream);
+        case 4: return launch_cols_few_rows<R, W, 4>(x, batch, cols, out, scale, stream);
+        case 5: return launch_cols_few_rows<R, W, 5>(x, batch, cols, out, scale, stream);
+        case 6: return launch_cols_few_rows<R, W, 6>(x, batch, cols, out, scale, stream);
+        case 7: return launch_cols_few_rows<R, W, 7>(x, batch, cols, out, scale, stream);
+        default: return launch_cols_few_rows<R, W, 8>(x, batch, cols, out, scale, stream);
     }
 }
 
@@ -1312,6 +1427,17 @@ static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t
     if (info == nullptr) return status;
 
     const bool vec = aligned16(x) && cols % 4 == 0;
+    if (rows <= kFewRows && xc.world == 0) {
+        const bool vec_few = vec && aligned16(out);  // this kernel also stores 128 bits at a time
+        const float few_scale = op == FDL_REDUCE_MEAN ? static_cast<float>(1.0 / mean_divisor) : 1.0f;
+        cudaStream_t st = as_stream(stream);
+        if (op == FDL_REDUCE_MAX) {
+            return vec_few ? launch_cols_few<ColMax, 4>(x, batch, rows, cols, out, few_scale, st)
+                       : launch_cols_few<ColMax, 1>(x, batch, rows, cols, out, few_scale, st);
+        }
+        return vec_few ? launch_cols_few<ColSum, 4>(x, batch, rows, cols, out, few_scale, st)
+                   : launch_cols_few<ColSum, 1>(x, batch, rows, cols, out, few_scale, st);
+    }
     ColsGeometry g;
     status = cols_geometry(info->sm_count, batch, rows, cols, vec, &g);
     if (status != FDL_OK) return status;

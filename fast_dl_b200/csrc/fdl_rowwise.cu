@@ -23,8 +23,10 @@
 // Rows of 16384 < cols <= 131072 floats are shared by a thread-block cluster of 2, 4 or 8
 // CTAs: each keeps a slice in registers and the row statistics cross the cluster through
 // distributed shared memory, so such a row is still read once and written once.
-// Rows that are unaligned, not a multiple of 4 floats, or longer than that take a
-// plain three-pass kernel (second and third pass hit L2).
+// Longer rows are cut into 32 KiB segments: one kernel leaves per-segment statistics and
+// combines them per row, a second applies them (two reads, one write).
+// Rows that are unaligned or not a multiple of 4 floats take a plain three-pass kernel
+// (second and third pass hit L2 while a row fits there).
 //
 // The one mbarrier wait is bounded; if it runs out the CTA raises a flag in host-visible
 // memory (fdl_take_device_error) and leaves without touching the output.
@@ -373,6 +375,178 @@ rows_staged_kernel(const RowParams p) {
     }
 }
 
+// ---- split form: rows longer than a cluster can hold -------------------------------------------
+//
+// Two kernels.  The first cuts every row into 32 KiB segments, one CTA each (grid = segments x
+// rows): the CTA keeps its segment in registers, leaves the segment's statistics in the
+// workspace -- softmax: (max, sum of exp(x - max)); layernorm: (mean, sum of squared
+// deviations from it) -- and the last CTA of a row to arrive (ticket counter) combines the
+// segments' statistics into the row's: softmax rescales each sum to the row maximum,
+// layernorm uses the pairwise update of Chan et al., both in a fixed order.  The second kernel
+// applies them elementwise.  Two reads and one write per element instead of one and one, against
+// the three passes (two of them out of L2 only while a row fits there) of the plain kernel.
+
+constexpr int kSplitThreads = 256;
+constexpr int kSplitNV = 8;
+constexpr int kSplitSegVecs = kSplitThreads * kSplitNV;  // 2048 packs = 32 KiB
+constexpr int64_t kSplitMaxRows = kWorkspaceCounterBytes / 4;
+
+template <class Op>
+__global__ void __launch_bounds__(kSplitThreads)
+rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats, unsigned int* counters) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    __shared__ float red[kMaxWarps];
+    __shared__ bool is_last;
+    const int64_t row = blockIdx.y;
+    const int seg = blockIdx.x;
+    const int nseg = gridDim.x;
+    const int nvec = p.cols / 4;
+    const int voff = seg * kSplitSegVecs;
+    int local = nvec - voff;
+    if (local > kSplitSegVecs) local = kSplitSegVecs;
+    const int t = threadIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols) + voff;
+    float4 v[kSplitNV];
+#pragma unroll
+    for (int i = 0; i < kSplitNV; ++i) {
+        if (t + i * kSplitThreads < local) v[i] = ld_stream(src + t + i * kSplitThreads);
+    }
+    float a = kSoftmax ? -INFINITY : 0.0f;
+#pragma unroll
+    for (int i = 0; i < kSplitNV; ++i) {
+        if (t + i * kSplitThreads < local) {
+            if (kSoftmax) a = fmaxf(a, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            else a += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    if (kSoftmax) a = team_max<kSplitThreads, kSplitThreads>(a, red);
+    else a = team_sum<kSplitThreads, kSplitThreads>(a, red) / static_cast<float>(local * 4);
+    float b = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kSplitNV; ++i) {
+        if (t + i * kSplitThreads < local) {
+            if (kSoftmax) {
+                b += (fast_exp2((v[i].x - a) * kLog2e) + fast_exp2((v[i].y - a) * kLog2e)) +
+                     (fast_exp2((v[i].z - a) * kLog2e) + fast_exp2((v[i].w - a) * kLog2e));
+            } else {
+                const float dx = v[i].x - a, dy = v[i].y - a, dz = v[i].z - a, dw = v[i].w - a;
+                b += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+            }
+        }
+    }
+    b = team_sum<kSplitThreads, kSplitThreads>(b, red);
+    if (t == 0) {
+        seg_stats[row * nseg + seg] = make_float2(a, b);
+        __threadfence();
+        const unsigned int ticket = atomicAdd(counters + row, 1u);
+        is_last = ticket == static_cast<unsigned int>(nseg - 1);
+        if (is_last) counters[row] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // Combine the segments' statistics; thread k takes segments k, k + 256, ... in order.
+    const float2* mine = seg_stats + row * nseg;
+    if (kSoftmax) {
+        float m = -INFINITY;
+        for (int k = t; k < nseg; k += kSplitThreads) m = fmaxf(m, __ldcg(&mine[k].x));
+        m = team_max<kSplitThreads, kSplitThreads>(m, red);
+        float s = 0.0f;
+        for (int k = t; k < nseg; k += kSplitThreads) {
+            s += __ldcg(&mine[k].y) * fast_exp2((__ldcg(&mine[k].x) - m) * kLog2e);
+        }
+        s = team_sum<kSplitThreads, kSplitThreads>(s, red);
+        if (t == 0) row_stats[row] = make_float2(m, 1.0f / s);
+    } else {
+        // mean = sum n_k mean_k / N;  M2 = sum (M2_k + n_k (mean_k - mean)^2)
+        const float n_full = static_cast<float>(kSplitSegVecs * 4);
+        const float n_last = static_cast<float>((nvec - (nseg - 1) * kSplitSegVecs) * 4);
+        const float inv_n = 1.0f / static_cast<float>(p.cols);
+        float s = 0.0f;
+        for (int k = t; k < nseg; k += kSplitThreads) s += (k == nseg - 1 ? n_last : n_full) * __ldcg(&mine[k].x);
+        const float mean = team_sum<kSplitThreads, kSplitThreads>(s, red) * inv_n;
+        float q = 0.0f;
+        for (int k = t; k < nseg; k += kSplitThreads) {
+            const float d = __ldcg(&mine[k].x) - mean;
+            q += __ldcg(&mine[k].y) + (k == nseg - 1 ? n_last : n_full) * d * d;
+        }
+        const float var = team_sum<kSplitThreads, kSplitThreads>(q, red) * inv_n;
+        const float rstd = 1.0f / sqrtf(var + p.eps);
+        if (t == 0) {
+            row_stats[row] = make_float2(mean, rstd);
+            if (p.mean_out != nullptr) p.mean_out[row] = mean;
+            if (p.rstd_out != nullptr) p.rstd_out[row] = rstd;
+        }
+    }
+}
+
+template <class Op>
+__global__ void __launch_bounds__(kSplitThreads)
+rows_split_apply_kernel(const RowParams p, const float2* row_stats) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int64_t row = blockIdx.y;
+    const int nvec = p.cols / 4;
+    const int voff = blockIdx.x * kSplitSegVecs;
+    int local = nvec - voff;
+    if (local > kSplitSegVecs) local = kSplitSegVecs;
+    const int t = threadIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols) + voff;
+    float4* dst = reinterpret_cast<float4*>(p.y + row * p.cols) + voff;
+    float4 v[kSplitNV];
+#pragma unroll
+    for (int i = 0; i < kSplitNV; ++i) {
+        if (t + i * kSplitThreads < local) v[i] = ld_stream(src + t + i * kSplitThreads);
+    }
+    const float2 st = row_stats[row];
+    const float4* g4 = p.gamma == nullptr ? nullptr : reinterpret_cast<const float4*>(p.gamma) + voff;
+    const float4* b4 = p.beta == nullptr ? nullptr : reinterpret_cast<const float4*>(p.beta) + voff;
+#pragma unroll
+    for (int i = 0; i < kSplitNV; ++i) {
+        const int c = t + i * kSplitThreads;
+        if (c < local) {
+            float4 o;
+            if (kSoftmax) {
+                o = make_float4(fast_exp2((v[i].x - st.x) * kLog2e) * st.y, fast_exp2((v[i].y - st.x) * kLog2e) * st.y,
+                                fast_exp2((v[i].z - st.x) * kLog2e) * st.y, fast_exp2((v[i].w - st.x) * kLog2e) * st.y);
+            } else {
+                o = make_float4((v[i].x - st.x) * st.y, (v[i].y - st.x) * st.y, (v[i].z - st.x) * st.y,
+                                (v[i].w - st.x) * st.y);
+                if (g4 != nullptr) {
+                    const float4 g = __ldg(g4 + c);
+                    o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;
+                }
+                if (b4 != nullptr) {
+                    const float4 b = __ldg(b4 + c);
+                    o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                }
+            }
+            st_stream(dst + c, o);
+        }
+    }
+}
+
+template <class Op>
+int launch_rows_split(const RowParams& p, cudaStream_t stream) {
+    const int64_t nvec = p.cols / 4;
+    const int64_t nseg = ceil_div(nvec, static_cast<int64_t>(kSplitSegVecs));
+    const size_t seg_bytes = static_cast<size_t>(p.rows) * nseg * sizeof(float2);
+    const size_t row_bytes = ((static_cast<size_t>(p.rows) * sizeof(float2) + 255) / 256) * 256;
+    void* scratch = nullptr;
+    const int status = get_workspace(kWorkspaceCounterBytes + row_bytes + seg_bytes, &scratch);
+    if (status != FDL_OK) return status;
+    unsigned int* counters = static_cast<unsigned int*>(scratch);
+    float2* row_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes);
+    float2* seg_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes + row_bytes);
+    const dim3 grid(static_cast<unsigned int>(nseg), static_cast<unsigned int>(p.rows));
+    rows_split_stats_kernel<Op><<<grid, kSplitThreads, 0, stream>>>(p, seg_stats, row_stats, counters);
+    int st = launch_status();
+    if (st != FDL_OK) return st;
+    rows_split_apply_kernel<Op><<<grid, kSplitThreads, 0, stream>>>(p, row_stats);
+    return launch_status();
+}
+
 // ---- plain fallback: one CTA per row, three passes ---------------------------------------
 
 constexpr int kPlainThreads = 256;
@@ -506,6 +680,9 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
         if (p.cols <= 2 * kCtaMaxCols) return launch_cluster_cfg<Op, 2>(p, stream);
         if (p.cols <= 4 * kCtaMaxCols) return launch_cluster_cfg<Op, 4>(p, stream);
         return launch_cluster_cfg<Op, 8>(p, stream);
+    }
+    if (packs && p.cols > 8 * kCtaMaxCols && p.rows <= kSplitMaxRows && p.rows <= 65535) {
+        return launch_rows_split<Op>(p, stream);
     }
     const bool in_registers = packs && p.cols <= kCtaMaxCols;
     if (in_registers) {

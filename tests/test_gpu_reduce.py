@@ -123,7 +123,8 @@ def test_argmax_ties_nan_inf(fdl, cuda):
     assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, x), fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "max with nan")
 
 
-@pytest.mark.parametrize("rows,cols", SHAPES + [(8192, 256), (100000, 4), (3, 5000000), (2, 4500001), (200000, 32)])
+@pytest.mark.parametrize("rows,cols", SHAPES + [(8192, 256), (100000, 4), (3, 5000000), (2, 4500001), (200000, 32),
+                                                (1, 1000), (8, 4096), (7, 130001), (9, 4096), (400000, 8), (150000, 36)])
 def test_column_reductions(fdl, cuda, rows, cols):
     rng = np.random.default_rng(42)
     x = rng.normal(size=(rows, cols)).astype(np.float32)
@@ -161,6 +162,20 @@ def test_column_reduction_batched_and_caller_scratch(fdl, cuda):
     scratch = cuda.zeros(max(nbytes, 256), dtype=cuda.uint8, device="cuda")
     for _ in range(2):
         assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN, scratch=scratch)), got, "caller scratch")
+
+
+def test_column_reduction_batched_few_rows_and_many_chunks(fdl, cuda):
+    """Batched matrices of a handful of rows (the no-tree kernel) and a tall narrow one whose
+    row chunks are folded by all thread rows of the last CTA."""
+    rng = np.random.default_rng(4)
+    for shape in ((6, 5, 1000), (3, 8, 4100), (4, 2, 37), (2, 300000, 16), (3, 100000, 40)):
+        x = rng.normal(size=shape).astype(np.float32)
+        xd = dev(cuda, x)
+        norm = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
+        assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), orc.reduce_cols(x, 0), norm, f"sum {shape}")
+        assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN)), orc.reduce_cols(x, 1), norm / shape[1], f"mean {shape}")
+        assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX)), orc.reduce_cols(x, 2), f"max {shape}")
+        assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "same bits")
 
 
 def test_config3_shapes(fdl, cuda):

@@ -11,7 +11,9 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(1, 1), (2, 4), (3, 5), (7, 128), (100, 132), (33, 1000), (64, 1024), (4096, 1024), (65, 2048),
           (37, 2052), (19, 4096), (11, 8192), (5, 16384), (3, 16388), (2, 40000), (1001, 36), (50000, 8),
           # rows shared by a cluster of 2, 4, 8 CTAs; beyond 131072 floats and odd lengths: the plain kernel
-          (5, 32768), (9, 32772), (3, 65536), (4, 100000), (2, 131072), (2, 131076), (3, 50001)]
+          (5, 32768), (9, 32772), (3, 65536), (4, 100000), (2, 131072), (2, 131076), (3, 50001),
+          # longer still: segments + per-row combination (two kernels)
+          (3, 262144), (5, 200004), (2, 1 << 20), (1, 3000000), (2, 131077)]
 
 
 def dev(cuda, a):
