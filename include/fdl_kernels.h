@@ -260,7 +260,12 @@ int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, 
                         void* stream);
 
 /* out[r] = lowest column index of the row maximum (NaN compares as -inf).  int64
- * output.  No counterpart in the reference. */
+ * output.  No counterpart in the reference.
+ * Both row reductions pick a kernel by shape: teams of lanes with several rows in flight for
+ * rows of up to 256 floats, a warp or a CTA per row beyond, and -- for fewer than 1184 rows of
+ * at least 256 KiB -- one CTA per 64 KiB segment with the segments' results folded per row
+ * through the library's per-device workspace (allocated on first use; such calls must not
+ * overlap on the GPU with other calls that use the workspace). */
 int fdl_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, int64_t* out,
                         void* stream);
 
@@ -277,7 +282,11 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
 
 /* y[r, c] = exp(x[r, c] - max_r) * (1 / sum_c exp(x[r, c] - max_r)).  Replaces
  * dl::kernels::softmax for every SoftmaxAlgo value (include/dl/kernels/softmax.hpp:15-16,
- * src/kernels/cuda/softmax.cu:28-254,272-285). */
+ * src/kernels/cuda/softmax.cu:28-254,272-285).
+ * Both row-wise normalisations read a row once and write it once up to 131072 floats per row
+ * (registers of one CTA up to 16384, of a thread-block cluster of 2, 4 or 8 CTAs beyond);
+ * longer rows take two kernels (per-segment statistics combined per row through the library's
+ * workspace, then applied: two reads, one write). */
 int fdl_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols,
                          void* stream);
 
