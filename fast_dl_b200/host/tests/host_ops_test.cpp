@@ -158,6 +158,53 @@ int main() {
                          dl::ops::relu(dl::ops::linear(ta, w, bias)).to_host<float>()));
     }
 
+    {   // shapes that take the other kernels: short rows, a few very long rows, a handful of rows
+        struct Case { int64_t rows, cols; };
+        const Case cases[] = {{5000, 16}, {300, 128}, {3, 400000}, {4, 40000}, {2, 262144}};
+        bool ok_red = true, ok_norm = true;
+        for (const Case& k : cases) {
+            const auto x = randoms(k.rows * k.cols, 11, -3, 3);
+            dl::Tensor tx = dl::Tensor::from_host<float>(x, dl::Shape({k.rows, k.cols}), dev);
+            std::vector<float> rs(k.rows), cm(k.cols), sm(k.rows * k.cols), ln(k.rows * k.cols);
+            std::vector<int64_t> am(k.rows);
+            std::vector<double> colsum(k.cols, 0.0);
+            for (int64_t r = 0; r < k.rows; ++r) {
+                const float* xr = x.data() + r * k.cols;
+                double s = 0, e = 0, q = 0;
+                float m = xr[0];
+                int64_t arg = 0;
+                for (int64_t c = 0; c < k.cols; ++c) {
+                    s += xr[c];
+                    colsum[c] += xr[c];
+                    if (xr[c] > m) { m = xr[c]; arg = c; }
+                }
+                const double mean = s / k.cols;
+                for (int64_t c = 0; c < k.cols; ++c) {
+                    e += std::exp(static_cast<double>(xr[c]) - m);
+                    q += (xr[c] - mean) * (xr[c] - mean);
+                }
+                const double rstd = 1.0 / std::sqrt(q / k.cols + 1e-5);
+                for (int64_t c = 0; c < k.cols; ++c) {
+                    sm[r * k.cols + c] = static_cast<float>(std::exp(static_cast<double>(xr[c]) - m) / e);
+                    ln[r * k.cols + c] = static_cast<float>((xr[c] - mean) * rstd);
+                }
+                rs[r] = static_cast<float>(s);
+                am[r] = arg;
+            }
+            for (int64_t c = 0; c < k.cols; ++c) cm[c] = static_cast<float>(colsum[c] / k.rows);
+            // sums of n terms of size <= 3: allow 1e-5 of the terms' scale, not of a sum that may be near zero
+            const float sum_tol = 1e-5f * 3.0f * std::sqrt(static_cast<float>(k.cols));
+            const auto got_rs = dl::ops::sum(tx, 1).to_host<float>();
+            for (int64_t r = 0; r < k.rows; ++r) ok_red = ok_red && std::fabs(got_rs[r] - rs[r]) <= sum_tol;
+            ok_red = ok_red && dl::ops::argmax(tx, 1).to_host<int64_t>() == am;
+            ok_red = ok_red && close(dl::ops::mean(tx, 0).to_host<float>(), cm, 1e-5f);
+            ok_norm = ok_norm && close(dl::ops::softmax(tx).to_host<float>(), sm, 1e-5f);
+            ok_norm = ok_norm && close(dl::ops::layernorm(tx).to_host<float>(), ln, 1e-5f);
+        }
+        report("reductions on short rows, a few long rows and a handful of rows", ok_red);
+        report("softmax and layernorm on rows of 16 ... 262144 floats", ok_norm);
+    }
+
     {   // the allocator hands blocks back out instead of calling cudaMalloc again
         const auto before = dl::allocator::stats();
         for (int i = 0; i < 50; ++i) dl::Tensor tmp = ta + ta;
