@@ -15,7 +15,12 @@ def dev(cuda, a):
 
 
 def random_matrix_shape(rng):
-    kind = rng.integers(0, 4)
+    kind = rng.integers(0, 6)
+    if kind == 4:   # a few very long rows: the segmented reductions, the cluster and two-kernel row forms
+        return int(rng.integers(1, 7)), int(rng.choice([20000, 40004, 100000, 131072, 200001, 262148, 400000]))
+    if kind == 5:   # a handful of rows, or very short ones
+        return (int(rng.integers(1, 9)), int(rng.integers(1, 300000))) if rng.integers(0, 2) else \
+               (int(rng.integers(1, 200000)), int(rng.choice([1, 2, 4, 8, 12, 16, 32, 33, 64, 100, 128, 256])))
     if kind == 0:
         return int(rng.integers(1, 64)), int(rng.integers(1, 70000))
     if kind == 1:
@@ -25,7 +30,7 @@ def random_matrix_shape(rng):
     return int(rng.integers(1, 40)), int(rng.integers(1, 40))
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5])
 def test_random_op_sequence(fdl, cuda, seed):
     rng = np.random.default_rng(seed)
     for step in range(40):
