@@ -25,8 +25,10 @@
 // distributed shared memory, so such a row is still read once and written once.
 // Longer rows are cut into 32 KiB segments: one kernel leaves per-segment statistics and
 // combines them per row, a second applies them (two reads, one write).
-// Rows that are unaligned or not a multiple of 4 floats take a plain three-pass kernel
-// (second and third pass hit L2 while a row fits there).
+// Rows whose length is not a multiple of 4 floats, or whose base is not 16-byte aligned, take
+// the masked form (128-bit accesses laid over the flat buffer, edge packs lane by lane) up to
+// 16384 floats; what is left (such rows beyond that, x and y at different phases) takes a plain
+// three-pass kernel (second and third pass hit L2 while a row fits there).
 //
 // The one mbarrier wait is bounded; if it runs out the CTA raises a flag in host-visible
 // memory (fdl_take_device_error) and leaves without touching the output.
@@ -235,6 +237,170 @@ rows_direct_kernel(const RowParams p) {
     }
     TeamScope<TPR, TH> scope{red};
     row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, row, active, scope);
+}
+
+// ---- masked form: rows whose length is not a multiple of 4 floats (or whose base is not 16-byte
+// aligned) ----------------------------------------------------------------------------------------
+//
+// Such rows start at any of the four phases of a 16-byte line, so the 128-bit loads are laid over
+// the FLAT buffer instead: a row is covered by the aligned packs [first_pack, first_pack + npk) of
+// the buffer, of which the first and the last may belong to the row only in part.  Interior
+// packs are loaded and stored as 128 bits exactly like in the direct form; the (at most two)
+// edge packs of a row are loaded and stored one valid float at a time -- they share their
+// 16 bytes with a neighbouring row that another team writes -- and their foreign lanes hold
+// values that cannot change the statistics (-inf for softmax; 0, then the row mean, for
+// layernorm).  x and y must sit at the same phase (their addresses agree modulo 16).
+
+struct RowEdges {
+    int head;  // floats of the first pack that precede the row (0..3)
+    int npk;   // aligned packs that cover the row
+    int cols;
+    // bit k set: lane k of pack `pi` belongs to the row
+    __device__ __forceinline__ int valid(int pi) const {
+        int first = head - pi * 4;
+        int last = head + cols - pi * 4;
+        first = first < 0 ? 0 : first;
+        last = last > 4 ? 4 : last;
+        return ((1 << last) - 1) & ~((1 << first) - 1);
+    }
+};
+
+__device__ __forceinline__ float& lane_of(float4& q, int k) {
+    return k == 0 ? q.x : (k == 1 ? q.y : (k == 2 ? q.z : q.w));
+}
+
+template <class Op, int TPR, int TH, int NV>
+__global__ void __launch_bounds__(TH, min_ctas_for(TH, NV))
+rows_masked_kernel(const RowParams p, int phase) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    __shared__ float red[kMaxWarps];
+    constexpr int kTeams = TH / TPR;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    const bool active = row < p.rows;
+    if (TPR >= kWarp && !active) return;
+    // position of the row in units of floats from the 16-byte line that holds x[0]
+    const int64_t e0 = phase + (active ? row : 0) * p.cols;
+    RowEdges edge;
+    edge.head = static_cast<int>(e0 & 3);
+    edge.cols = p.cols;
+    edge.npk = (edge.head + p.cols + 3) >> 2;
+    const float* xline = p.x - phase;  // 16-byte aligned
+    float* yline = p.y - phase;
+    const float4* src = reinterpret_cast<const float4*>(xline) + (e0 >> 2);
+    float4* dst = reinterpret_cast<float4*>(yline) + (e0 >> 2);
+    const float neutral = kSoftmax ? -INFINITY : 0.0f;
+
+    float4 v[NV];
+    int okv[NV];  // which lanes of pack i belong to the row
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int pi = t + i * TPR;
+        okv[i] = (active && pi < edge.npk) ? edge.valid(pi) : 0;
+        if (pi < edge.npk) {
+            const int ok = okv[i];
+            if (ok == 15) {
+                v[i] = ld_stream(src + pi);
+            } else {
+                v[i] = make_float4(neutral, neutral, neutral, neutral);
+                const float* q = reinterpret_cast<const float*>(src + pi);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (ok & (1 << k)) lane_of(v[i], k) = ld_stream(q + k);
+                }
+            }
+        }
+    }
+    // first statistic: row maximum / row mean
+    float a = neutral;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (t + i * TPR < edge.npk) {
+            if (kSoftmax) a = fmaxf(a, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            else a += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    const float inv_n = 1.0f / static_cast<float>(p.cols);
+    if (kSoftmax) a = team_max<TPR, TH>(a, red);
+    else a = team_sum<TPR, TH>(a, red) * inv_n;
+    // second statistic: sum of exp(x - max) / sum of squared deviations
+    float b = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int pi = t + i * TPR;
+        if (pi < edge.npk) {
+            if (kSoftmax) {
+                v[i].x = fast_exp2((v[i].x - a) * kLog2e);
+                v[i].y = fast_exp2((v[i].y - a) * kLog2e);
+                v[i].z = fast_exp2((v[i].z - a) * kLog2e);
+                v[i].w = fast_exp2((v[i].w - a) * kLog2e);
+                b += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            } else {
+                const int ok = okv[i];
+                if (ok != 15) {  // foreign lanes sit on the mean: no deviation
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (!(ok & (1 << k))) lane_of(v[i], k) = a;
+                    }
+                }
+                const float dx = v[i].x - a, dy = v[i].y - a, dz = v[i].z - a, dw = v[i].w - a;
+                b += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+            }
+        }
+    }
+    b = team_sum<TPR, TH>(b, red);
+    if (!active) return;
+    const float scale = kSoftmax ? 1.0f / b : 1.0f / sqrtf(b * inv_n + p.eps);
+    if (!kSoftmax && t == 0) {
+        if (p.mean_out != nullptr) p.mean_out[row] = a;
+        if (p.rstd_out != nullptr) p.rstd_out[row] = scale;
+    }
+    const bool affine = !kSoftmax && (p.gamma != nullptr || p.beta != nullptr);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int pi = t + i * TPR;
+        if (pi < edge.npk) {
+            float4 o;
+            if (kSoftmax) {
+                o = make_float4(v[i].x * scale, v[i].y * scale, v[i].z * scale, v[i].w * scale);
+            } else {
+                o = make_float4((v[i].x - a) * scale, (v[i].y - a) * scale, (v[i].z - a) * scale,
+                                (v[i].w - a) * scale);
+                if (affine) {
+                    const int c0 = pi * 4 - edge.head;  // column of lane 0 (negative on a head pack)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (okv[i] & (1 << k)) {
+                            if (p.gamma != nullptr) lane_of(o, k) *= __ldg(p.gamma + c0 + k);
+                            if (p.beta != nullptr) lane_of(o, k) += __ldg(p.beta + c0 + k);
+                        }
+                    }
+                }
+            }
+            const int ok = okv[i];
+            if (ok == 15) {
+                st_stream(dst + pi, o);
+            } else {
+                float* q = reinterpret_cast<float*>(dst + pi);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (ok & (1 << k)) st_stream(q + k, lane_of(o, k));
+                }
+            }
+        }
+    }
+}
+
+template <class Op, int TPR, int TH, int NV>
+int launch_masked_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream) {
+    constexpr int kTeams = TH / TPR;
+    const int64_t grid = ceil_div(p.rows, kTeams);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
+    rows_masked_kernel<Op, TPR, TH, NV><<<static_cast<unsigned int>(grid), TH, 0, stream>>>(p, phase);
+    return launch_status();
 }
 
 // ---- staged form: one bulk copy per CTA ---------------------------------------------------------
@@ -716,9 +882,10 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
 }
 
 // Picks the team size and the registers-per-thread bucket for a row length.
-#define FDL_ROW_DISPATCH(LAUNCH)                                                         \
+#define FDL_ROW_DISPATCH(LAUNCH) FDL_ROW_DISPATCH_N(LAUNCH, p.cols / 4)
+#define FDL_ROW_DISPATCH_N(LAUNCH, NVEC)                                                 \
     do {                                                                                 \
-        const int nvec_ = p.cols / 4;                                                    \
+        const int nvec_ = (NVEC);                                                        \
         if (nvec_ <= 8) return LAUNCH<Op, 8, 256, 1>(p, info, stream);                   \
         if (nvec_ <= 16) return LAUNCH<Op, 16, 256, 1>(p, info, stream);                 \
         if (nvec_ <= 32) return LAUNCH<Op, 32, 256, 1>(p, info, stream);                 \
@@ -760,6 +927,14 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     }
     if (packs && p.cols > 8 * kCtaMaxCols && p.rows <= kSplitMaxRows && p.rows <= 65535) {
         return launch_rows_split<Op>(p, stream);
+    }
+    // Rows at any phase of a 16-byte line (length not a multiple of 4, or a base that is not
+    // 16-byte aligned): the masked form, as long as x and y share the phase and a row's packs
+    // fit one CTA's registers.
+    const int64_t packs_worst = (static_cast<int64_t>(p.cols) + 6) / 4;
+    if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
+        packs_worst <= kCtaMaxCols / 4) {
+        FDL_ROW_DISPATCH_N(launch_masked_cfg, static_cast<int>(packs_worst));
     }
     const bool in_registers = packs && p.cols <= kCtaMaxCols;
     if (in_registers) {
