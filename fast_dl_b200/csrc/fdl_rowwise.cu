@@ -634,9 +634,21 @@ constexpr int kSplitNV = 8;
 constexpr int kSplitSegVecs = kSplitThreads * kSplitNV;  // 2048 packs = 32 KiB
 constexpr int64_t kSplitMaxRows = kWorkspaceCounterBytes / 4;
 
-template <class Op>
+// Both kernels address a row through the aligned packs of the flat buffer (RowEdges, as in the
+// masked form), so rows of any length and phase qualify; MASKED = false compiles the edge
+// handling away for rows that are whole packs.
+
+__device__ __forceinline__ int split_count(const RowEdges& e, int seg) {
+    // floats of the row inside segment `seg`
+    const int lo = max(e.head, seg * kSplitSegVecs * 4);
+    const int hi = min(e.head + e.cols, (seg + 1) * kSplitSegVecs * 4);
+    return hi > lo ? hi - lo : 0;
+}
+
+template <class Op, bool MASKED>
 __global__ void __launch_bounds__(kSplitThreads)
-rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats, unsigned int* counters) {
+rows_split_stats_kernel(const RowParams p, int phase, float2* seg_stats, float2* row_stats,
+                        unsigned int* counters) {
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
     constexpr float kLog2e = 1.4426950408889634f;
     __shared__ float red[kMaxWarps];
@@ -644,18 +656,37 @@ rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats,
     const int64_t row = blockIdx.y;
     const int seg = blockIdx.x;
     const int nseg = gridDim.x;
-    const int nvec = p.cols / 4;
+    const int64_t e0 = phase + row * p.cols;
+    RowEdges edge;
+    edge.head = MASKED ? static_cast<int>(e0 & 3) : 0;
+    edge.cols = p.cols;
+    edge.npk = (edge.head + p.cols + 3) >> 2;
     const int voff = seg * kSplitSegVecs;
-    int local = nvec - voff;
+    int local = edge.npk - voff;
     if (local > kSplitSegVecs) local = kSplitSegVecs;
     const int t = threadIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols) + voff;
+    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + voff;
+    const float neutral = kSoftmax ? -INFINITY : 0.0f;
     float4 v[kSplitNV];
+    int okv[kSplitNV];
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
-        if (t + i * kSplitThreads < local) v[i] = ld_stream(src + t + i * kSplitThreads);
+        const int li = t + i * kSplitThreads;
+        okv[i] = li < local ? (MASKED ? edge.valid(voff + li) : 15) : 0;
+        if (li < local) {
+            if (okv[i] == 15) {
+                v[i] = ld_stream(src + li);
+            } else {
+                v[i] = make_float4(neutral, neutral, neutral, neutral);
+                const float* q = reinterpret_cast<const float*>(src + li);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (okv[i] & (1 << k)) lane_of(v[i], k) = ld_stream(q + k);
+                }
+            }
+        }
     }
-    float a = kSoftmax ? -INFINITY : 0.0f;
+    float a = neutral;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
         if (t + i * kSplitThreads < local) {
@@ -663,8 +694,9 @@ rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats,
             else a += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     }
+    const int count = split_count(edge, seg);
     if (kSoftmax) a = team_max<kSplitThreads, kSplitThreads>(a, red);
-    else a = team_sum<kSplitThreads, kSplitThreads>(a, red) / static_cast<float>(local * 4);
+    else a = team_sum<kSplitThreads, kSplitThreads>(a, red) / static_cast<float>(count > 0 ? count : 1);
     float b = 0.0f;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
@@ -673,12 +705,19 @@ rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats,
                 b += (fast_exp2((v[i].x - a) * kLog2e) + fast_exp2((v[i].y - a) * kLog2e)) +
                      (fast_exp2((v[i].z - a) * kLog2e) + fast_exp2((v[i].w - a) * kLog2e));
             } else {
+                if (MASKED && okv[i] != 15) {  // foreign lanes sit on the mean
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (!(okv[i] & (1 << k))) lane_of(v[i], k) = a;
+                    }
+                }
                 const float dx = v[i].x - a, dy = v[i].y - a, dz = v[i].z - a, dw = v[i].w - a;
                 b += (dx * dx + dy * dy) + (dz * dz + dw * dw);
             }
         }
     }
     b = team_sum<kSplitThreads, kSplitThreads>(b, red);
+    if (kSoftmax && count == 0) b = 0.0f;  // an empty segment: exp(-inf - -inf) is not a number
     if (t == 0) {
         seg_stats[row * nseg + seg] = make_float2(a, b);
         __threadfence();
@@ -697,22 +736,23 @@ rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats,
         m = team_max<kSplitThreads, kSplitThreads>(m, red);
         float s = 0.0f;
         for (int k = t; k < nseg; k += kSplitThreads) {
-            s += __ldcg(&mine[k].y) * fast_exp2((__ldcg(&mine[k].x) - m) * kLog2e);
+            const float sk = __ldcg(&mine[k].y);
+            if (sk != 0.0f) s += sk * fast_exp2((__ldcg(&mine[k].x) - m) * kLog2e);
         }
         s = team_sum<kSplitThreads, kSplitThreads>(s, red);
         if (t == 0) row_stats[row] = make_float2(m, 1.0f / s);
     } else {
         // mean = sum n_k mean_k / N;  M2 = sum (M2_k + n_k (mean_k - mean)^2)
-        const float n_full = static_cast<float>(kSplitSegVecs * 4);
-        const float n_last = static_cast<float>((nvec - (nseg - 1) * kSplitSegVecs) * 4);
         const float inv_n = 1.0f / static_cast<float>(p.cols);
         float s = 0.0f;
-        for (int k = t; k < nseg; k += kSplitThreads) s += (k == nseg - 1 ? n_last : n_full) * __ldcg(&mine[k].x);
+        for (int k = t; k < nseg; k += kSplitThreads) {
+            s += static_cast<float>(split_count(edge, k)) * __ldcg(&mine[k].x);
+        }
         const float mean = team_sum<kSplitThreads, kSplitThreads>(s, red) * inv_n;
         float q = 0.0f;
         for (int k = t; k < nseg; k += kSplitThreads) {
             const float d = __ldcg(&mine[k].x) - mean;
-            q += __ldcg(&mine[k].y) + (k == nseg - 1 ? n_last : n_full) * d * d;
+            q += __ldcg(&mine[k].y) + static_cast<float>(split_count(edge, k)) * d * d;
         }
         const float var = team_sum<kSplitThreads, kSplitThreads>(q, red) * inv_n;
         const float rstd = 1.0f / sqrtf(var + p.eps);
@@ -724,31 +764,51 @@ rows_split_stats_kernel(const RowParams p, float2* seg_stats, float2* row_stats,
     }
 }
 
-template <class Op>
+template <class Op, bool MASKED>
 __global__ void __launch_bounds__(kSplitThreads)
-rows_split_apply_kernel(const RowParams p, const float2* row_stats) {
+rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
     constexpr float kLog2e = 1.4426950408889634f;
     const int64_t row = blockIdx.y;
-    const int nvec = p.cols / 4;
+    const int64_t e0 = phase + row * p.cols;
+    RowEdges edge;
+    edge.head = MASKED ? static_cast<int>(e0 & 3) : 0;
+    edge.cols = p.cols;
+    edge.npk = (edge.head + p.cols + 3) >> 2;
     const int voff = blockIdx.x * kSplitSegVecs;
-    int local = nvec - voff;
+    int local = edge.npk - voff;
     if (local > kSplitSegVecs) local = kSplitSegVecs;
     const int t = threadIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.cols) + voff;
-    float4* dst = reinterpret_cast<float4*>(p.y + row * p.cols) + voff;
+    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + voff;
+    float4* dst = reinterpret_cast<float4*>(p.y - phase) + (e0 >> 2) + voff;
     float4 v[kSplitNV];
+    int okv[kSplitNV];
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
-        if (t + i * kSplitThreads < local) v[i] = ld_stream(src + t + i * kSplitThreads);
+        const int li = t + i * kSplitThreads;
+        okv[i] = li < local ? (MASKED ? edge.valid(voff + li) : 15) : 0;
+        if (li < local) {
+            if (okv[i] == 15) {
+                v[i] = ld_stream(src + li);
+            } else {
+                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float* q = reinterpret_cast<const float*>(src + li);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (okv[i] & (1 << k)) lane_of(v[i], k) = ld_stream(q + k);
+                }
+            }
+        }
     }
     const float2 st = row_stats[row];
-    const float4* g4 = p.gamma == nullptr ? nullptr : reinterpret_cast<const float4*>(p.gamma) + voff;
-    const float4* b4 = p.beta == nullptr ? nullptr : reinterpret_cast<const float4*>(p.beta) + voff;
+    const bool affine = !kSoftmax && (p.gamma != nullptr || p.beta != nullptr);
+    // gamma / beta line up with the packs (and can be read 128 bits at a time)
+    const bool affine_packs = (!MASKED || edge.head == 0) &&
+                              ((reinterpret_cast<uintptr_t>(p.gamma) | reinterpret_cast<uintptr_t>(p.beta)) & 15u) == 0;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
-        const int c = t + i * kSplitThreads;
-        if (c < local) {
+        const int li = t + i * kSplitThreads;
+        if (li < local) {
             float4 o;
             if (kSoftmax) {
                 o = make_float4(fast_exp2((v[i].x - st.x) * kLog2e) * st.y, fast_exp2((v[i].y - st.x) * kLog2e) * st.y,
@@ -756,24 +816,46 @@ rows_split_apply_kernel(const RowParams p, const float2* row_stats) {
             } else {
                 o = make_float4((v[i].x - st.x) * st.y, (v[i].y - st.x) * st.y, (v[i].z - st.x) * st.y,
                                 (v[i].w - st.x) * st.y);
-                if (g4 != nullptr) {
-                    const float4 g = __ldg(g4 + c);
-                    o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;
-                }
-                if (b4 != nullptr) {
-                    const float4 b = __ldg(b4 + c);
-                    o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                if (affine) {
+                    const int c0 = (voff + li) * 4 - edge.head;
+                    if (affine_packs && okv[i] == 15) {
+                        if (p.gamma != nullptr) {
+                            const float4 g = __ldg(reinterpret_cast<const float4*>(p.gamma + c0));
+                            o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;
+                        }
+                        if (p.beta != nullptr) {
+                            const float4 bb = __ldg(reinterpret_cast<const float4*>(p.beta + c0));
+                            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (okv[i] & (1 << k)) {
+                                if (p.gamma != nullptr) lane_of(o, k) *= __ldg(p.gamma + c0 + k);
+                                if (p.beta != nullptr) lane_of(o, k) += __ldg(p.beta + c0 + k);
+                            }
+                        }
+                    }
                 }
             }
-            st_stream(dst + c, o);
+            if (okv[i] == 15) {
+                st_stream(dst + li, o);
+            } else {
+                float* q = reinterpret_cast<float*>(dst + li);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (okv[i] & (1 << k)) st_stream(q + k, lane_of(o, k));
+                }
+            }
         }
     }
 }
 
-template <class Op>
+template <class Op, bool MASKED>
 int launch_rows_split(const RowParams& p, cudaStream_t stream) {
-    const int64_t nvec = p.cols / 4;
-    const int64_t nseg = ceil_div(nvec, static_cast<int64_t>(kSplitSegVecs));
+    const int phase = MASKED ? static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u) : 0;
+    const int64_t npk = MASKED ? (static_cast<int64_t>(p.cols) + 6) / 4 : p.cols / 4;
+    const int64_t nseg = ceil_div(npk, static_cast<int64_t>(kSplitSegVecs));
     const size_t seg_bytes = static_cast<size_t>(p.rows) * nseg * sizeof(float2);
     const size_t row_bytes = ((static_cast<size_t>(p.rows) * sizeof(float2) + 255) / 256) * 256;
     void* scratch = nullptr;
@@ -783,10 +865,10 @@ int launch_rows_split(const RowParams& p, cudaStream_t stream) {
     float2* row_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes);
     float2* seg_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes + row_bytes);
     const dim3 grid(static_cast<unsigned int>(nseg), static_cast<unsigned int>(p.rows));
-    rows_split_stats_kernel<Op><<<grid, kSplitThreads, 0, stream>>>(p, seg_stats, row_stats, counters);
+    rows_split_stats_kernel<Op, MASKED><<<grid, kSplitThreads, 0, stream>>>(p, phase, seg_stats, row_stats, counters);
     int st = launch_status();
     if (st != FDL_OK) return st;
-    rows_split_apply_kernel<Op><<<grid, kSplitThreads, 0, stream>>>(p, row_stats);
+    rows_split_apply_kernel<Op, MASKED><<<grid, kSplitThreads, 0, stream>>>(p, phase, row_stats);
     return launch_status();
 }
 
@@ -926,7 +1008,7 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
         return launch_cluster_cfg<Op, 8>(p, stream);
     }
     if (packs && p.cols > 8 * kCtaMaxCols && p.rows <= kSplitMaxRows && p.rows <= 65535) {
-        return launch_rows_split<Op>(p, stream);
+        return launch_rows_split<Op, false>(p, stream);
     }
     // Rows at any phase of a 16-byte line (length not a multiple of 4, or a base that is not
     // 16-byte aligned): the masked form, as long as x and y share the phase and a row's packs
@@ -935,6 +1017,10 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
         packs_worst <= kCtaMaxCols / 4) {
         FDL_ROW_DISPATCH_N(launch_masked_cfg, static_cast<int>(packs_worst));
+    }
+    if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
+        p.rows <= kSplitMaxRows && p.rows <= 65535) {
+        return launch_rows_split<Op, true>(p, stream);  // longer rows at any phase: the two-kernel form
     }
     const bool in_registers = packs && p.cols <= kCtaMaxCols;
     if (in_registers) {

@@ -162,7 +162,8 @@ def test_direct_and_staged_forms_agree(fdl, cuda, rows, cols):
         assert np.array_equal(out[-1][k].view(np.uint32), out[picked][k].view(np.uint32))
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 1024), (100, 1001), (1000, 63), (7, 4096), (9, 8190), (5, 16380)])
+@pytest.mark.parametrize("rows,cols", [(64, 1024), (100, 1001), (1000, 63), (7, 4096), (9, 8190), (5, 16380),
+                                       (3, 40001), (2, 20000), (2, 140002)])
 @pytest.mark.parametrize("x_off,y_off", [(1, 1), (3, 3), (2, 2), (1, 2), (0, 1)])
 def test_rows_at_any_phase_of_a_16_byte_line(fdl, cuda, rows, cols, x_off, y_off):
     """Views whose base is not 16-byte aligned: same phase for x and y (the masked form) and
