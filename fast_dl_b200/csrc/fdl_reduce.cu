@@ -466,6 +466,7 @@ struct SumRed {
     __device__ static State combine(State a, State b) { return a + b; }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
     __device__ static State load_cg(const State* p) { return __ldcg(p); }  // L2, never a stale L1 line
+    __device__ static State shift(State a, int) { return a; }
     __device__ static Out finish(State a, int64_t, float) { return a; }
 };
 struct MeanRed : SumRed {
@@ -480,6 +481,7 @@ struct MaxRed {
     __device__ static State combine(State a, State b) { return fmaxf(a, b); }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
     __device__ static State load_cg(const State* p) { return __ldcg(p); }
+    __device__ static State shift(State a, int) { return a; }
     __device__ static Out finish(State a, int64_t, float) { return a; }
 };
 struct ArgState {
@@ -502,6 +504,8 @@ struct ArgmaxRed {
         return ArgState{__shfl_xor_sync(kFullMask, a.v, o), __shfl_xor_sync(kFullMask, a.i, o)};
     }
     __device__ static State load_cg(const State* p) { return ArgState{__ldcg(&p->v), __ldcg(&p->i)}; }
+    // columns counted from the start of the row's first pack -> columns of the row
+    __device__ static State shift(State a, int head) { return ArgState{a.v, a.i == INT_MAX ? a.i : a.i - head}; }
     __device__ static Out finish(State a, int64_t, float) {
         return a.i == INT_MAX ? 0 : static_cast<int64_t>(a.i);
     }
@@ -594,11 +598,45 @@ __device__ __forceinline__ typename R::State thread_reduce_span(const float* xr,
     return R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
 }
 
+// The same for a row at ANY phase of a 16-byte line (length not a multiple of 4 floats, or a
+// base that is not 16-byte aligned): the row is covered by aligned packs of the flat buffer,
+// the full ones go through thread_reduce_span as 128-bit loads, and the (at most two) packs
+// that belong to the row only in part are read float by float by lanes 0 and 1.  Columns are
+// counted from the start of the first pack (R::shift takes `head` off again at the end).
+// [pk_begin, pk_end) limits the work to a segment of the row, in packs.
+template <class R, int STRIDE>
+__device__ __forceinline__ typename R::State thread_reduce_flat(const float* x, int phase, int64_t row,
+                                                                 int cols, int t, int pk_begin, int pk_end,
+                                                                 int* head_out) {
+    using State = typename R::State;
+    const int64_t e0 = phase + row * cols;
+    const int head = static_cast<int>(e0 & 3);
+    const int npk = (head + cols + 3) >> 2;
+    const int tail = (head + cols) & 3;  // floats of the row in a partial last pack (0: it is full)
+    const float* line = (x - phase) + (e0 - head);
+    const int full_lo = head ? 1 : 0;
+    const int full_hi = tail ? npk - 1 : npk;
+    const int lo = full_lo > pk_begin ? full_lo : pk_begin;
+    const int hi = full_hi < pk_end ? full_hi : pk_end;
+    State s = thread_reduce_span<R, 4, STRIDE>(line, lo + t, hi);
+    if (t == 0 && head && pk_begin == 0) {
+        const int stop = head + cols < 4 ? head + cols : 4;
+        for (int k = head; k < stop; ++k) s = R::combine(s, R::lift(ld_stream(line + k), k));
+    }
+    if (t == 1 && tail && !(npk == 1 && head) && npk - 1 >= pk_begin && npk - 1 < pk_end) {
+        const int base = (npk - 1) * 4;
+        for (int k = 0; k < tail; ++k) s = R::combine(s, R::lift(ld_stream(line + base + k), base + k));
+    }
+    *head_out = head;
+    return s;
+}
+
 // TPR threads cooperate on a row (32: one warp per row, 8 rows per CTA; 256: one CTA per
-// row).  W = 4 needs cols % 4 == 0 and a 16-byte aligned base.
+// row).  W = 4 needs cols % 4 == 0 and a 16-byte aligned base; W = 1 takes rows at any phase
+// (thread_reduce_flat), `phase` being the position of x[0] in its 16-byte line, in floats.
 template <class R, int TPR, int W>
 __global__ void __launch_bounds__(kRowThreads)
-reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out, float divisor) {
+reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out, float divisor, int phase) {
     using State = typename R::State;
     constexpr int kRowsPerCta = kRowThreads / TPR;
     __shared__ State red[kRowThreads / kWarp];
@@ -610,11 +648,13 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
 
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + team; row < rows;
          row += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
-        State s = thread_reduce_span<R, W, TPR>(x + row * cols, t, npack);
+        int head = 0;
+        State s = W == 4 ? thread_reduce_span<R, 4, TPR>(x + row * cols, t, npack)
+                         : thread_reduce_flat<R, TPR>(x, phase, row, cols, t, 0, INT_MAX, &head);
 #pragma unroll
         for (int o = kWarp / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
         if (TPR == kWarp) {
-            if (lane == 0) out[row] = R::finish(s, cols, divisor);
+            if (lane == 0) out[row] = R::finish(R::shift(s, head), cols, divisor);
         } else {
             // One CTA per row: every thread of the CTA runs the same trip count.
             if (lane == 0) red[warp] = s;
@@ -623,7 +663,7 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
                 State z = lane < kRowThreads / kWarp ? red[lane] : R::identity();
 #pragma unroll
                 for (int o = kWarp / 2; o > 0; o >>= 1) z = R::combine(z, R::shuffle_xor(z, o));
-                if (lane == 0) out[row] = R::finish(z, cols, divisor);
+                if (lane == 0) out[row] = R::finish(R::shift(z, head), cols, divisor);
             }
             __syncthreads();
         }
@@ -794,7 +834,7 @@ int launch_rows_narrow(const float* x, int64_t rows, int64_t cols, typename R::O
 template <class R, int W>
 __global__ void __launch_bounds__(kRowThreads)
 reduce_rows_split_kernel(const float* x, int cols, int seg_items, typename R::State* partials,
-                         unsigned int* counters, typename R::Out* out, float divisor) {
+                         unsigned int* counters, typename R::Out* out, float divisor, int phase) {
     using State = typename R::State;
     __shared__ State red[kRowThreads / kWarp];
     __shared__ bool is_last;
@@ -808,7 +848,10 @@ reduce_rows_split_kernel(const float* x, int cols, int seg_items, typename R::St
     int end = begin + seg_items;
     if (end > nitem) end = nitem;
 
-    State s = thread_reduce_span<R, W, kRowThreads>(x + row * cols, begin + static_cast<int>(threadIdx.x), end);
+    int head = 0;
+    State s = W == 4 ? thread_reduce_span<R, 4, kRowThreads>(x + row * cols, begin + static_cast<int>(threadIdx.x), end)
+                     : thread_reduce_flat<R, kRowThreads>(x, phase, row, cols, static_cast<int>(threadIdx.x), begin,
+                                                          begin + seg_items, &head);
     auto cta_fold = [&](State z) {
 #pragma unroll
         for (int o = kWarp / 2; o > 0; o >>= 1) z = R::combine(z, R::shuffle_xor(z, o));
@@ -835,7 +878,7 @@ reduce_rows_split_kernel(const float* x, int cols, int seg_items, typename R::St
     const State* mine = partials + row * nseg;
     for (int k = threadIdx.x; k < nseg; k += kRowThreads) z = R::combine(z, R::load_cg(mine + k));
     z = cta_fold(z);
-    if (threadIdx.x == 0) out[row] = R::finish(z, cols, divisor);
+    if (threadIdx.x == 0) out[row] = R::finish(R::shift(z, head), cols, divisor);
 }
 
 constexpr int64_t kSplitMaxRows = 1184;               // below 8 CTAs per SM of a B200
@@ -847,11 +890,13 @@ template <class R, int W>
 int launch_rows_split(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
                       cudaStream_t stream) {
     using State = typename R::State;
-    const int64_t nitem = cols / W;
+    // W = 4: packs of an aligned row.  W = 1: a row at any phase, also cut in (flat, aligned) packs;
+    // one more than cols / 4 may be needed to cover it.
+    const int64_t nitem = W == 4 ? cols / 4 : (cols + 6) / 4;
     int64_t nseg = ceil_div(cols * 4, kSplitSegmentBytes);
     if (nseg > kSplitMaxSegments) nseg = kSplitMaxSegments;
     // whole 128-byte lines per segment, so that segments of a row do not share a line
-    const int64_t line_items = 128 / (4 * W);
+    const int64_t line_items = 8;
     const int64_t seg_items = ceil_div(ceil_div(nitem, nseg), line_items) * line_items;
     nseg = ceil_div(nitem, seg_items);
     void* scratch = nullptr;
@@ -863,7 +908,7 @@ int launch_rows_split(const float* x, int64_t rows, int64_t cols, typename R::Ou
     const dim3 grid(static_cast<unsigned int>(nseg), static_cast<unsigned int>(rows));
     reduce_rows_split_kernel<R, W><<<grid, kRowThreads, 0, stream>>>(
         x, static_cast<int>(cols), static_cast<int>(seg_items), partials, counters, out,
-        static_cast<float>(cols));
+        static_cast<float>(cols), static_cast<int>((reinterpret_cast<uintptr_t>(x) & 15u) / 4u));
     return launch_status();
 }
 
@@ -874,8 +919,9 @@ int launch_rows_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out*
     // One CTA per group of rows; the block scheduler balances them over the SMs.
     int64_t grid = ceil_div(rows, kRowsPerCta);
     if (grid > 2147483647) grid = 2147483647;
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(x) & 15u) / 4u);
     reduce_rows_kernel<R, TPR, W><<<static_cast<unsigned int>(grid), kRowThreads, 0, stream>>>(
-        x, rows, static_cast<int>(cols), out, static_cast<float>(cols));
+        x, rows, static_cast<int>(cols), out, static_cast<float>(cols), phase);
     return launch_status();
 }
 
