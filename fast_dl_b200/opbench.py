@@ -197,6 +197,17 @@ def main(ref=None) -> None:
             record("shp", f"full sum of {k} elements", 4 * k + 4, lambda k=k: capi.full_sum(flat[:k]))
         del X, out
 
+    if "odd" in cfgs:  # row lengths that are not a multiple of 4 floats: every row at another phase of a 16-byte line
+        for R, C in ((65536, 1001), (65536, 1023), (8192, 50257), (4096, 8191), (1 << 20, 63), (262144, 255)):
+            L = normal((R, C), 3.0)
+            out = torch.empty_like(L)
+            record("odd", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
+            record("odd", f"layernorm [{R},{C}]", 8 * R * C, lambda: capi.layernorm_rows(L, out=out))
+            record("odd", f"sum axis 1 [{R},{C}]", 4 * R * C + 4 * R, lambda: capi.reduce_rows(L, capi.REDUCE_SUM))
+            record("odd", f"argmax axis 1 [{R},{C}]", 4 * R * C + 8 * R, lambda: capi.argmax_rows(L))
+            record("odd", f"mean axis 0 [{R},{C}]", 4 * R * C + 4 * C, lambda: capi.reduce_cols(L, capi.REDUCE_MEAN))
+            del L, out
+
     if "c5" in cfgs:
         n, C = 1 << 28, 16384
         x, y = uniform(n), uniform(n)
