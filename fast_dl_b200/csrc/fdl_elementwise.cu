@@ -316,6 +316,97 @@ broadcast_kernel(F f, const __grid_constant__ BroadcastPlan plan, const float* a
     }
 }
 
+// ---- dense operand at a row length that is not a multiple of 4 ------------------------------------
+//
+// When one operand has the output's own (contiguous) layout, it and the output can be walked
+// as aligned 128-bit packs of the FLAT buffer whatever the extents are; only the other,
+// broadcast operand needs an index per element.  The plan is in elements (W = 1).  A pack
+// that stays inside one innermost run takes one decomposition (the common case: 4 / extent
+// of the packs cross a run boundary); one that crosses takes four.  The broadcast operand's
+// floats come through the default cache path: they are re-read by many packs.
+template <class F, bool DENSE_IS_A>
+__global__ void __launch_bounds__(kEwThreads)
+broadcast_flat_kernel(F f, const __grid_constant__ BroadcastPlan plan, const float* dense,
+                      const float* other, float* out, uint32_t n) {
+    constexpr uint32_t kTile = kEwThreads * kEwUnroll;
+    const uint32_t full = n >> 2;
+    const uint32_t base = blockIdx.x * kTile + threadIdx.x;
+    const int64_t other_inner = DENSE_IS_A ? plan.b_inner : plan.a_inner;
+    Pack<4> xd[kEwUnroll], xo[kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+        const uint32_t item = base + u * kEwThreads;
+        if (item < full) {
+            xd[u] = load_pack<4>(dense, item);
+            const uint32_t e = item * 4;
+            int64_t ao, bo;
+            decompose<1>(plan, e, &ao, &bo);
+            const int64_t o0 = DENSE_IS_A ? bo : ao;
+            const uint32_t run = fast_divide(e, plan.inner_div);
+            const uint32_t in_run = e - run * plan.inner_div.d;
+            if (in_run + 3 < plan.inner_div.d) {
+                if (other_inner == 0) {
+                    const float v = other[o0];
+                    xo[u] = Pack<4>{{v, v, v, v}};
+                } else {
+                    xo[u] = Pack<4>{{other[o0], other[o0 + other_inner], other[o0 + 2 * other_inner],
+                                    other[o0 + 3 * other_inner]}};
+                }
+            } else if (plan.inner_div.d >= 4) {
+                // One run boundary inside the pack: a second decomposition for the first
+                // element behind it, the rest by the inner stride again.
+                const uint32_t before = plan.inner_div.d - in_run;  // 1..3 elements of this run
+                decompose<1>(plan, e + before, &ao, &bo);
+                const int64_t o1 = DENSE_IS_A ? bo : ao;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int64_t off = static_cast<uint32_t>(k) < before
+                                            ? o0 + k * other_inner
+                                            : o1 + (k - static_cast<int>(before)) * other_inner;
+                    xo[u].v[k] = other[off];
+                }
+            } else {
+                xo[u].v[0] = other[o0];
+#pragma unroll
+                for (int k = 1; k < 4; ++k) {
+                    decompose<1>(plan, e + k, &ao, &bo);
+                    xo[u].v[k] = other[DENSE_IS_A ? bo : ao];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+        const uint32_t item = base + u * kEwThreads;
+        if (item < full) {
+            store_pack<4>(out, item, DENSE_IS_A ? apply<4>(f, xd[u], xo[u], xd[u]) : apply<4>(f, xo[u], xd[u], xd[u]));
+        }
+    }
+    // the last n % 4 elements, one thread
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        for (uint32_t e = full * 4; e < n; ++e) {
+            int64_t ao, bo;
+            decompose<1>(plan, e, &ao, &bo);
+            const Pack<1> d{{dense[e]}};
+            const Pack<1> o{{other[DENSE_IS_A ? bo : ao]}};
+            out[e] = (DENSE_IS_A ? apply<1>(f, d, o, d) : apply<1>(f, o, d, d)).v[0];
+        }
+    }
+}
+
+template <class F>
+int launch_broadcast_flat(const F& f, const BroadcastPlan& plan, bool dense_is_a, const float* dense,
+                          const float* other, float* out, uint32_t n, cudaStream_t stream) {
+    int64_t tiles = ceil_div(static_cast<int64_t>(n >> 2), static_cast<int64_t>(kEwThreads) * kEwUnroll);
+    if (tiles < 1) tiles = 1;
+    if (dense_is_a) {
+        broadcast_flat_kernel<F, true><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(f, plan, dense, other, out, n);
+    } else {
+        broadcast_flat_kernel<F, false><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(f, plan, dense, other, out, n);
+    }
+    return launch_status();
+}
+
 template <int W, class F>
 int launch_broadcast_w(const F& f, const BroadcastPlan& plan, const float* a, const float* b,
                        float* out, cudaStream_t stream) {
@@ -417,6 +508,22 @@ int run_broadcast(const F& f, const float* a, const float* b, float* out, int nd
     const int64_t top_a = nd >= 2 ? dims[0].a : 0;
     const int64_t top_b = nd >= 2 ? dims[0].b : 0;
     const int64_t slab = kMaxPacks / packs_per_top;
+    // Not 128-bit-able dimension by dimension, but one operand has the output's own layout:
+    // 128-bit packs over the flat buffers, the other operand indexed per element.
+    if (!vec && top_size <= slab && total < (int64_t{1} << 31) && aligned16(out)) {
+        bool a_dense = aligned16(a), b_dense = aligned16(b);
+        int64_t expect = 1;
+        for (int i = nd - 1; i >= 0; --i) {
+            if (dims[i].a != expect) a_dense = false;
+            if (dims[i].b != expect) b_dense = false;
+            expect *= dims[i].size;
+        }
+        if (a_dense || b_dense) {
+            plan.total_packs = static_cast<uint32_t>(total);
+            return launch_broadcast_flat<F>(f, plan, a_dense, a_dense ? a : b, a_dense ? b : a, out,
+                                            static_cast<uint32_t>(total), stream);
+        }
+    }
     for (int64_t start = 0; start < top_size; start += slab) {
         const int64_t count = top_size - start < slab ? top_size - start : slab;
         plan.total_packs = static_cast<uint32_t>(count * packs_per_top);

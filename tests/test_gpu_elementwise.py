@@ -144,7 +144,12 @@ def test_binary_bit_exact_vs_reference_gpu_kernels(fdl, cuda, op):
 
 BCAST = [((4096, 4096), (1, 4096)), ((4096, 4096), (4096, 1)), ((33, 70), (1, 70)), ((33, 70), (33, 1)),
          ((7, 5, 12), (5, 1)), ((3, 1, 8), (1, 6, 1)), ((6, 4), (4,)), ((2, 3, 4, 5, 6), (1, 3, 1, 5, 1)),
-         ((1,), (5, 3)), ((5, 3), (1,)), ((64, 1), (1, 64)), ((9, 8), (9, 8))]
+         ((1,), (5, 3)), ((5, 3), (1,)), ((64, 1), (1, 64)), ((9, 8), (9, 8)),
+         # extents that are not multiples of 4: 128-bit packs over the flat buffers of the dense operand and
+         # the output, the broadcast operand per element (packs that cross a row, tails of 1-3 elements)
+         ((1001, 1001), (1, 1001)), ((1001, 1001), (1001, 1)), ((1001,), (777, 1001)), ((333, 1), (333, 1023)),
+         ((5, 63, 7, 9), (1, 63, 1, 1)), ((37, 3), (3,)), ((37, 3), (37, 1)), ((2, 2, 2, 3), (2, 1, 2, 1)),
+         ((1023, 5), (1,)), ((7,), (1,)), ((3, 1), (3, 2)), ((64, 1023, 31), (1023, 1)), ((50001,), (1,))]
 
 
 @pytest.mark.parametrize("sa,sb", BCAST)
@@ -169,7 +174,7 @@ def test_config2_bias_then_scale(fdl, cuda):
     assert_bit_exact(got, ((A + b).astype(np.float32) * s).astype(np.float32), "config 2")
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 5), (128, 1000), (1000, 4096)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 5), (128, 1000), (1000, 4096), (999, 1001), (4096, 63)])
 def test_row_bias_in_place(fdl, cuda, rows, cols):
     rng = np.random.default_rng(45)
     x = rng.normal(size=(rows, cols)).astype(np.float32)
