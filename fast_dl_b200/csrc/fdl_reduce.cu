@@ -979,12 +979,20 @@ __global__ void __launch_bounds__(kColThreads)
 reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float* partials,
                    unsigned int* counters, int tx, int rows_per_chunk, float scale,
                    const ColsExchange xc) {
-    extern __shared__ float tile[];  // [TY][TX*W]
+    // Every thread owns C = 4 columns of the CTA's tile of tx * 4: with W = 4 four adjacent
+    // ones (one 128-bit load per row), with W = 1 -- column counts that are not a multiple of
+    // 4, unaligned bases -- the columns cx, cx + tx, cx + 2 tx, cx + 3 tx (four coalesced 32-bit
+    // loads per row), so that either way a thread has 8 x 16 bytes outstanding.
+    constexpr int C = 4;
+    extern __shared__ float tile[];  // [TY][TX*C]
     __shared__ bool is_last;
     const int ty_count = kColThreads / tx;
     const int cx = threadIdx.x % tx;
     const int ry = threadIdx.x / tx;
-    const int64_t col = (static_cast<int64_t>(blockIdx.x) * tx + cx) * W;
+    const int tile_w = tx * C;
+    const int64_t col0 = static_cast<int64_t>(blockIdx.x) * tile_w;
+    const int64_t col = col0 + (W == 4 ? cx * 4 : cx);  // first of the thread's columns
+    const int cstep = W == 4 ? 1 : tx;                      // distance between them
     const int chunk = blockIdx.y;
     const int nchunks = gridDim.y;
     const int64_t b = blockIdx.z;
@@ -992,11 +1000,11 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
 
     constexpr int kInFlight = 8;  // rows in flight per thread: 32 KiB requested per CTA at a time
     constexpr int kAcc = 2;
-    float acc[kAcc][W];
+    float acc[kAcc][C];
 #pragma unroll
     for (int u = 0; u < kAcc; ++u) {
 #pragma unroll
-        for (int k = 0; k < W; ++k) acc[u][k] = R::identity();
+        for (int k = 0; k < C; ++k) acc[u][k] = R::identity();
     }
 
     const int64_t r_begin = static_cast<int64_t>(chunk) * rows_per_chunk;
@@ -1004,46 +1012,51 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     if (r_end > rows) r_end = rows;
     if (col < cols) {
         const float* xc = xb + col;
+        bool have[C];  // W = 1: which of the four columns exist (the last tile may be ragged)
+#pragma unroll
+        for (int k = 0; k < C; ++k) have[k] = W == 4 || col + k * cstep < cols;
         int64_t r = r_begin + ry;
         for (; r + (kInFlight - 1) * ty_count < r_end; r += kInFlight * ty_count) {
-            float v[kInFlight][W];
+            float v[kInFlight][C];
 #pragma unroll
             for (int u = 0; u < kInFlight; ++u) {
                 const float* src = xc + (r + u * ty_count) * cols;
                 if (W == 4) {
                     const float4 t = ld_stream(reinterpret_cast<const float4*>(src));
-                    v[u][0] = t.x; v[u][1 % W] = t.y; v[u][2 % W] = t.z; v[u][3 % W] = t.w;
+                    v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
                 } else {
-                    v[u][0] = ld_stream(src);
+#pragma unroll
+                    for (int k = 0; k < C; ++k) v[u][k] = have[k] ? ld_stream(src + k * cstep) : R::identity();
                 }
             }
 #pragma unroll
             for (int u = 0; u < kInFlight; ++u) {
 #pragma unroll
-                for (int k = 0; k < W; ++k) acc[u % kAcc][k] = R::combine(acc[u % kAcc][k], v[u][k]);
+                for (int k = 0; k < C; ++k) acc[u % kAcc][k] = R::combine(acc[u % kAcc][k], v[u][k]);
             }
         }
         for (; r < r_end; r += ty_count) {
             const float* src = xc + r * cols;
             if (W == 4) {
                 const float4 t = ld_stream(reinterpret_cast<const float4*>(src));
-                acc[0][0] = R::combine(acc[0][0], t.x); acc[0][1 % W] = R::combine(acc[0][1 % W], t.y);
-                acc[0][2 % W] = R::combine(acc[0][2 % W], t.z); acc[0][3 % W] = R::combine(acc[0][3 % W], t.w);
+                acc[0][0] = R::combine(acc[0][0], t.x); acc[0][1] = R::combine(acc[0][1], t.y);
+                acc[0][2] = R::combine(acc[0][2], t.z); acc[0][3] = R::combine(acc[0][3], t.w);
             } else {
-                acc[0][0] = R::combine(acc[0][0], ld_stream(src));
+#pragma unroll
+                for (int k = 0; k < C; ++k) {
+                    if (have[k]) acc[0][k] = R::combine(acc[0][k], ld_stream(src + k * cstep));
+                }
             }
         }
     }
-    const int tile_w = tx * W;
 #pragma unroll
-    for (int k = 0; k < W; ++k) {
-        tile[ry * tile_w + cx * W + k] = R::combine(acc[0][k], acc[1][k]);
+    for (int k = 0; k < C; ++k) {
+        tile[ry * tile_w + (W == 4 ? cx * 4 + k : k * tx + cx)] = R::combine(acc[0][k], acc[1][k]);
     }
     __syncthreads();
 
     // Fold the TY rows of the tile (fixed order): thread c owns column c and leaves the
     // CTA's value for it in tile[c].
-    const int64_t col0 = static_cast<int64_t>(blockIdx.x) * tile_w;
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
         float s = tile[c];
         for (int y = 1; y < ty_count; ++y) s = R::combine(s, tile[y * tile_w + c]);
@@ -1107,44 +1120,51 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     // the result does not depend on which group came last, and no thread walks more than
     // groups / TY partials however many row chunks the matrix was cut into.
     {
-        float s[W];
+        float s[C];
 #pragma unroll
-        for (int k = 0; k < W; ++k) s[k] = R::identity();
+        for (int k = 0; k < C; ++k) s[k] = R::identity();
         if (col < cols) {
             const float* src = partials + b * cols + col;
             const int64_t stride = static_cast<int64_t>(gridDim.z) * cols;
+            bool have[C];
+#pragma unroll
+            for (int k = 0; k < C; ++k) have[k] = W == 4 || col + k * cstep < cols;
             int g = ry;
             for (; g + 3 * ty_count < groups; g += 4 * ty_count) {
-                float v[4][W];
+                float v[4][C];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float* q = src + (g + j * ty_count) * stride;
                     if (W == 4) {
                         const float4 t = __ldcg(reinterpret_cast<const float4*>(q));
-                        v[j][0] = t.x; v[j][1 % W] = t.y; v[j][2 % W] = t.z; v[j][3 % W] = t.w;
+                        v[j][0] = t.x; v[j][1] = t.y; v[j][2] = t.z; v[j][3] = t.w;
                     } else {
-                        v[j][0] = __ldcg(q);
+#pragma unroll
+                        for (int k = 0; k < C; ++k) v[j][k] = have[k] ? __ldcg(q + k * cstep) : R::identity();
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                    for (int k = 0; k < W; ++k) s[k] = R::combine(s[k], v[j][k]);
+                    for (int k = 0; k < C; ++k) s[k] = R::combine(s[k], v[j][k]);
                 }
             }
             for (; g < groups; g += ty_count) {
                 const float* q = src + g * stride;
                 if (W == 4) {
                     const float4 t = __ldcg(reinterpret_cast<const float4*>(q));
-                    s[0] = R::combine(s[0], t.x); s[1 % W] = R::combine(s[1 % W], t.y);
-                    s[2 % W] = R::combine(s[2 % W], t.z); s[3 % W] = R::combine(s[3 % W], t.w);
+                    s[0] = R::combine(s[0], t.x); s[1] = R::combine(s[1], t.y);
+                    s[2] = R::combine(s[2], t.z); s[3] = R::combine(s[3], t.w);
                 } else {
-                    s[0] = R::combine(s[0], __ldcg(q));
+#pragma unroll
+                    for (int k = 0; k < C; ++k) {
+                        if (have[k]) s[k] = R::combine(s[k], __ldcg(q + k * cstep));
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int k = 0; k < W; ++k) tile[ry * tile_w + cx * W + k] = s[k];
+        for (int k = 0; k < C; ++k) tile[ry * tile_w + (W == 4 ? cx * 4 + k : k * tx + cx)] = s[k];
     }
     __syncthreads();
     for (int c = threadIdx.x; c < tile_w; c += kColThreads) {
@@ -1251,8 +1271,8 @@ struct ColsGeometry {
 
 int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool vec,
                   ColsGeometry* g) {
-    g->w = vec ? 4 : 1;
-    const int64_t packs = ceil_div(cols, g->w);
+    g->w = vec ? 4 : 1;  // load width; a thread owns four columns either way
+    const int64_t packs = ceil_div(cols, 4);
     int tx = 1;
     int tx_max = tuning().cols_tx;  // threads across columns (x4 floats = row bytes per CTA)
     // With few rows, thread rows beyond rows / 8 would sit idle: widen the tile instead (a
@@ -1504,7 +1524,7 @@ static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(g.col_blocks, g.chunks, static_cast<unsigned int>(batch));
     cfg.blockDim = dim3(kColThreads);
-    cfg.dynamicSmemBytes = static_cast<size_t>(kColThreads) * g.w * sizeof(float);
+    cfg.dynamicSmemBytes = static_cast<size_t>(kColThreads) * 4 * sizeof(float);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
