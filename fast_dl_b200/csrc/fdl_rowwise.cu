@@ -963,6 +963,18 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
     return launch_status();
 }
 
+// Rows of 257..512 packs: a 256-thread CTA per row leaves every thread one or two packs and
+// two CTA-wide barriers per statistic, which is slow at the low end of the range ([65536,1028]:
+// 69-76% of the copy bandwidth); a warp per row with up to 16 packs a lane measures 87-89%
+// there.  Layernorm is ahead with the warp form over the whole range (104% at 1536 and 2048
+// floats), softmax -- a warp then evaluates up to 2048 exponentials -- only up to 320 packs.
+template <class Op>
+bool warp_takes_16_packs(int nvec) {
+    const int mode = tuning().rows_warp16;  // -1: by measurement (default), 0: never, 1: always
+    if (mode >= 0) return mode == 1;
+    return std::is_same<Op, LayerNormOp>::value || nvec <= 320;
+}
+
 // Picks the team size and the registers-per-thread bucket for a row length.
 #define FDL_ROW_DISPATCH(LAUNCH) FDL_ROW_DISPATCH_N(LAUNCH, p.cols / 4)
 #define FDL_ROW_DISPATCH_N(LAUNCH, NVEC)                                                 \
@@ -974,6 +986,7 @@ int launch_staged_cfg(const RowParams& p, const DeviceInfo* info, cudaStream_t s
         if (nvec_ <= 64) return LAUNCH<Op, 32, 256, 2>(p, info, stream);                 \
         if (nvec_ <= 128) return LAUNCH<Op, 32, 256, 4>(p, info, stream);                \
         if (nvec_ <= 256) return LAUNCH<Op, 32, 256, 8>(p, info, stream);                \
+        if (nvec_ <= 512 && warp_takes_16_packs<Op>(nvec_)) return LAUNCH<Op, 32, 256, 16>(p, info, stream); \
         if (nvec_ <= 512) return LAUNCH<Op, 256, 256, 2>(p, info, stream);               \
         if (nvec_ <= 1024) return LAUNCH<Op, 256, 256, 4>(p, info, stream);              \
         if (nvec_ <= 2048) return LAUNCH<Op, 256, 256, 8>(p, info, stream);              \
