@@ -407,7 +407,8 @@ int launch_masked_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream
 
 // ---- cluster form: rows of 16384 < cols <= 8 x 16384 floats -----------------------------------------
 //
-// A thread-block cluster of CL CTAs (512 threads, 8 packs each) owns one row: CTA `rank`
+// A thread-block cluster of CL CTAs (256 threads up to 65536 floats, 512 beyond; 8 packs a
+// thread) owns one row: CTA `rank`
 // keeps slice `rank` of it in registers and reduces it on its own; thread 0 stores the
 // result into slot `rank` of EVERY CTA's shared memory (distributed shared memory) and after
 // ONE cluster barrier each CTA combines the CL slots in rank order.  Softmax exchanges
@@ -421,12 +422,11 @@ int launch_masked_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream
 constexpr int kClusterThreads = 512;
 constexpr int kClusterNV = 8;
 
-template <class Op, int CL>
-__global__ void __launch_bounds__(kClusterThreads, 2)
+template <class Op, int CL, int TH>
+__global__ void __launch_bounds__(TH, 2048 / TH / 2)
 rows_cluster_kernel(const RowParams p, int slice_vecs) {
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
     constexpr float kLog2e = 1.4426950408889634f;
-    constexpr int TH = kClusterThreads;
     __shared__ float red[kMaxWarps];
     __shared__ float slots[2][8];
     cg::cluster_group cluster = cg::this_cluster();
@@ -546,14 +546,14 @@ rows_cluster_kernel(const RowParams p, int slice_vecs) {
     }
 }
 
-template <class Op, int CL>
+template <class Op, int CL, int TH>
 int launch_cluster_cfg(const RowParams& p, cudaStream_t stream) {
     const int nvec = p.cols / 4;
     const int slice_vecs = static_cast<int>(ceil_div(static_cast<int64_t>(nvec), CL));
     if (p.rows * CL > 2147483647) return FDL_ERR_UNSUPPORTED;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned int>(p.rows * CL));
-    cfg.blockDim = dim3(kClusterThreads);
+    cfg.blockDim = dim3(TH);
     cfg.stream = stream;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -562,7 +562,7 @@ int launch_cluster_cfg(const RowParams& p, cudaStream_t stream) {
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, rows_cluster_kernel<Op, CL>, p, slice_vecs);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, rows_cluster_kernel<Op, CL, TH>, p, slice_vecs);
     if (e != cudaSuccess) return static_cast<int>(e);
     return launch_status();
 }
@@ -1016,9 +1016,15 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
                        (p.beta == nullptr || aligned16(p.beta));
     constexpr int kCtaMaxCols = kClusterThreads * kClusterNV * 4;  // 16384 floats in one CTA's registers
     if (packs && p.cols > kCtaMaxCols && p.cols <= 8 * kCtaMaxCols) {
-        if (p.cols <= 2 * kCtaMaxCols) return launch_cluster_cfg<Op, 2>(p, stream);
-        if (p.cols <= 4 * kCtaMaxCols) return launch_cluster_cfg<Op, 4>(p, stream);
-        return launch_cluster_cfg<Op, 8>(p, stream);
+        if (tuning().rows_cluster_threads == 256 && p.cols <= 4 * kCtaMaxCols) {
+            // 256-thread CTAs hold 8192 floats each: twice the CTAs per row, four resident per SM
+            // (measured 86-91% against 79-86% with 512-thread CTAs; 128-thread CTAs add nothing)
+            if (p.cols <= 2 * kCtaMaxCols) return launch_cluster_cfg<Op, 4, 256>(p, stream);
+            return launch_cluster_cfg<Op, 8, 256>(p, stream);
+        }
+        if (p.cols <= 2 * kCtaMaxCols) return launch_cluster_cfg<Op, 2, 512>(p, stream);
+        if (p.cols <= 4 * kCtaMaxCols) return launch_cluster_cfg<Op, 4, 512>(p, stream);
+        return launch_cluster_cfg<Op, 8, 512>(p, stream);
     }
     if (packs && p.cols > 8 * kCtaMaxCols && p.rows <= kSplitMaxRows && p.rows <= 65535) {
         return launch_rows_split<Op, false>(p, stream);

@@ -164,6 +164,10 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().cols_cluster = value;
         return FDL_OK;
     }
+    if (k == "rows_cluster_threads" && (value == 256 || value == 512)) {
+        fdl::tuning().rows_cluster_threads = value;
+        return FDL_OK;
+    }
     if (k == "rows_warp16" && value >= -1 && value <= 1) {
         fdl::tuning().rows_warp16 = value;
         return FDL_OK;

@@ -102,7 +102,8 @@ int fdl_take_device_error(void);
  * registers, 1 = staged through shared memory by one bulk-async copy per CTA, -1 = staged
  * for rows of up to 128 floats and direct beyond; default -1), "rows_warp16" (rows of
  * 1028..2048 floats: 1 = one warp per row with 16 packs a lane, 0 = a 256-thread CTA per row,
- * -1 = whichever measured faster for the op and length; default -1),
+ * -1 = whichever measured faster for the op and length; default -1), "rows_cluster_threads"
+ * (256 or 512 threads per CTA in the cluster form of rows of 16388..65536 floats; default 256),
  * and for the column reductions "cols_tx" (threads across columns per CTA: 16..256; default
  * 64), "cols_cluster" (1, 2, 4, 8; default 4), "cols_ctas_per_sm" (default 4) and
  * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default).
