@@ -30,7 +30,7 @@ def random_matrix_shape(rng):
     return int(rng.integers(1, 40)), int(rng.integers(1, 40))
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_random_op_sequence(fdl, cuda, seed):
     rng = np.random.default_rng(seed)
     for step in range(40):
@@ -39,8 +39,20 @@ def test_random_op_sequence(fdl, cuda, seed):
         if rows * cols > 3_000_000:
             rows = max(1, 3_000_000 // cols)
         x = rng.normal(0, 2, (rows, cols)).astype(np.float32)
-        xd = dev(cuda, x)
-        what = f"seed {seed} step {step} op {op} shape {rows}x{cols}"
+        # a third of the steps run on a view that starts 1..3 floats off the 16-byte grid
+        off = int(rng.integers(1, 4)) if rng.integers(0, 3) == 0 else 0
+        if off:
+            buf = cuda.zeros(rows * cols + 4, dtype=cuda.float32, device="cuda")
+            buf[off:off + rows * cols] = dev(cuda, x).reshape(-1)
+            xd = buf[off:off + rows * cols].view(rows, cols)
+        else:
+            xd = dev(cuda, x)
+
+        def like_x():   # an output at the same phase as the input view
+            o = cuda.full((rows * cols + 4,), np.float32(-7.0), dtype=cuda.float32, device="cuda")
+            return o, o[off:off + rows * cols].view(rows, cols)
+
+        what = f"seed {seed} step {step} op {op} shape {rows}x{cols} off {off}"
         x64 = x.astype(np.float64)
         if op == 0:
             y = rng.uniform(0.5, 2, (rows, cols)).astype(np.float32)
@@ -63,12 +75,19 @@ def test_random_op_sequence(fdl, cuda, seed):
         elif op == 4:
             assert_sum_close(to_np(fdl.full_sum(xd.reshape(-1)))[0], x64.sum(), np.sqrt((x64 ** 2).sum()), what)
         elif op == 5:
-            assert_close_scaled(to_np(fdl.softmax_rows(xd)), orc.softmax_rows_f64(x), what)
+            whole, view = like_x()
+            fdl.softmax_rows(xd, out=view)
+            assert_close_scaled(to_np(view), orc.softmax_rows_f64(x), what)
+            edge = to_np(whole)
+            assert (edge[:off] == -7.0).all() and (edge[off + rows * cols:] == -7.0).all(), what
         elif op == 6:
             g = rng.uniform(0.9, 1.1, cols).astype(np.float32)
             b = rng.uniform(-0.1, 0.1, cols).astype(np.float32)
-            got = to_np(fdl.layernorm_rows(xd, dev(cuda, g), dev(cuda, b)))
-            assert_close_scaled(got, orc.layernorm_rows_f64(x, g, b), what)
+            whole, view = like_x()
+            fdl.layernorm_rows(xd, dev(cuda, g), dev(cuda, b), out=view)
+            assert_close_scaled(to_np(view), orc.layernorm_rows_f64(x, g, b), what)
+            edge = to_np(whole)
+            assert (edge[:off] == -7.0).all() and (edge[off + rows * cols:] == -7.0).all(), what
         else:
             k = int(rng.integers(0, 5))
             got, want = to_np(fdl.unary(xd, k, 0.02)), orc.unary(x, k, 0.02).reshape(rows, cols)
