@@ -931,7 +931,7 @@ int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out
     if (rows < 0 || cols < 0) return FDL_ERR_INVALID_ARGUMENT;
     if (rows == 0) return FDL_OK;
     if (x == nullptr || out == nullptr || cols == 0) return FDL_ERR_INVALID_ARGUMENT;
-    if (cols >= INT_MAX) return FDL_ERR_UNSUPPORTED;
+    if (cols >= INT_MAX - 16) return FDL_ERR_UNSUPPORTED;  // pack arithmetic on a row stays inside int
     const bool vec = aligned16(x) && cols % 4 == 0;
     if ((vec ? cols / 4 : cols) <= kNarrowMaxItems) {
         return vec ? launch_rows_narrow<R, 4>(x, rows, cols, out, stream)
