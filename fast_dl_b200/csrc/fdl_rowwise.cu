@@ -393,6 +393,120 @@ rows_masked_kernel(const RowParams p, int phase) {
     }
 }
 
+// Short rows at any phase (up to 32 packs): a lane holds at most one pack of a row, so a team
+// of TPR lanes keeps U rows in flight at once (teams take interleaved rows, so that a warp's
+// loads stay contiguous).  Otherwise as rows_masked_kernel.
+template <class Op, int TPR, int U>
+__global__ void __launch_bounds__(256)
+rows_masked_short_kernel(const RowParams p, int phase) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr int kTeams = 256 / TPR;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * (kTeams * U) + team;
+    const float neutral = kSoftmax ? -INFINITY : 0.0f;
+    const float inv_n = 1.0f / static_cast<float>(p.cols);
+    float4 v[U];
+    int okv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        const int64_t e0 = phase + (row < p.rows ? row : 0) * p.cols;
+        RowEdges edge;
+        edge.head = static_cast<int>(e0 & 3);
+        edge.cols = p.cols;
+        edge.npk = (edge.head + p.cols + 3) >> 2;
+        okv[u] = (row < p.rows && t < edge.npk) ? edge.valid(t) : 0;
+        const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + t;
+        v[u] = make_float4(neutral, neutral, neutral, neutral);
+        if (okv[u] == 15) {
+            v[u] = ld_stream(src);
+        } else {
+            const float* q = reinterpret_cast<const float*>(src);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (okv[u] & (1 << k)) lane_of(v[u], k) = ld_stream(q + k);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t row = row0 + static_cast<int64_t>(u) * kTeams;
+        float a = kSoftmax ? fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w))
+                           : (v[u].x + v[u].y) + (v[u].z + v[u].w);
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(kFullMask, a, o);
+            a = kSoftmax ? fmaxf(a, other) : a + other;
+        }
+        if (!kSoftmax) a *= inv_n;
+        float b;
+        if (kSoftmax) {
+            v[u].x = fast_exp2((v[u].x - a) * kLog2e);
+            v[u].y = fast_exp2((v[u].y - a) * kLog2e);
+            v[u].z = fast_exp2((v[u].z - a) * kLog2e);
+            v[u].w = fast_exp2((v[u].w - a) * kLog2e);
+            b = (v[u].x + v[u].y) + (v[u].z + v[u].w);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (!(okv[u] & (1 << k))) lane_of(v[u], k) = a;  // foreign lanes sit on the mean
+            }
+            const float dx = v[u].x - a, dy = v[u].y - a, dz = v[u].z - a, dw = v[u].w - a;
+            b = (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) b += __shfl_xor_sync(kFullMask, b, o);
+        if (row >= p.rows) continue;
+        const float scale = kSoftmax ? 1.0f / b : 1.0f / sqrtf(b * inv_n + p.eps);
+        if (!kSoftmax && t == 0) {
+            if (p.mean_out != nullptr) p.mean_out[row] = a;
+            if (p.rstd_out != nullptr) p.rstd_out[row] = scale;
+        }
+        if (okv[u] == 0) continue;
+        const int64_t e0 = phase + row * p.cols;
+        const int head = static_cast<int>(e0 & 3);
+        float4 o4;
+        if (kSoftmax) {
+            o4 = make_float4(v[u].x * scale, v[u].y * scale, v[u].z * scale, v[u].w * scale);
+        } else {
+            o4 = make_float4((v[u].x - a) * scale, (v[u].y - a) * scale, (v[u].z - a) * scale,
+                             (v[u].w - a) * scale);
+            if (p.gamma != nullptr || p.beta != nullptr) {
+                const int c0 = t * 4 - head;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (okv[u] & (1 << k)) {
+                        if (p.gamma != nullptr) lane_of(o4, k) *= __ldg(p.gamma + c0 + k);
+                        if (p.beta != nullptr) lane_of(o4, k) += __ldg(p.beta + c0 + k);
+                    }
+                }
+            }
+        }
+        float4* dst = reinterpret_cast<float4*>(p.y - phase) + (e0 >> 2) + t;
+        if (okv[u] == 15) {
+            st_stream(dst, o4);
+        } else {
+            float* q = reinterpret_cast<float*>(dst);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (okv[u] & (1 << k)) st_stream(q + k, lane_of(o4, k));
+            }
+        }
+    }
+}
+
+template <class Op, int TPR>
+int launch_masked_short_cfg(const RowParams& p, cudaStream_t stream) {
+    constexpr int U = 4;
+    const int64_t grid = ceil_div(p.rows, static_cast<int64_t>(256 / TPR) * U);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
+    rows_masked_short_kernel<Op, TPR, U><<<static_cast<unsigned int>(grid), 256, 0, stream>>>(p, phase);
+    return launch_status();
+}
+
 template <class Op, int TPR, int TH, int NV>
 int launch_masked_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream) {
     constexpr int kTeams = TH / TPR;
@@ -1035,6 +1149,9 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     const int64_t packs_worst = (static_cast<int64_t>(p.cols) + 6) / 4;
     if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
         packs_worst <= kCtaMaxCols / 4) {
+        if (packs_worst <= 8) return launch_masked_short_cfg<Op, 8>(p, stream);
+        if (packs_worst <= 16) return launch_masked_short_cfg<Op, 16>(p, stream);
+        if (packs_worst <= 32) return launch_masked_short_cfg<Op, 32>(p, stream);
         FDL_ROW_DISPATCH_N(launch_masked_cfg, static_cast<int>(packs_worst));
     }
     if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
