@@ -29,7 +29,7 @@ def test_host_binary_unary_chain(fdl, cuda, n):
     assert_sum_close(s, orc.full_sum(a), max(orc.norm2(a), 1e-30), "host sum")
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 4), (100, 36), (3000, 4096), (700, 16384)])
+@pytest.mark.parametrize("rows,cols", [(1, 4), (100, 36), (3000, 4096), (700, 16384), (9001, 4096), (7, 1 << 20)])
 def test_host_sweep_and_row_broadcast(fdl, cuda, rows, cols):
     rng = np.random.default_rng(43)
     x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
