@@ -44,3 +44,21 @@ def test_product_does_not_import_the_oracle():
             if path.name == "build.py":
                 continue  # compiles the checker, does not use it
             assert "oracle" not in text, f"{path} mentions the oracle"
+
+
+def test_every_documented_tuning_key_is_accepted(fdl):
+    """The keys named in the header's description of fdl_set_tuning, each with its documented
+    default; an unknown key and an out-of-range value are refused.  No GPU involved."""
+    import re
+    header = (ROOT / "include" / "fdl_kernels.h").read_text()
+    doc = header[header.index("Measurement aid: selects a launch shape"):header.index("int fdl_set_tuning")]
+    keys = re.findall(r'"([a-z0-9_]+)"', doc)
+    defaults = {"sum_cluster": 4, "rows_staged": -1, "rows_warp16": -1, "rows_cluster_threads": 256,
+                "cols_tx": 64, "cols_cluster": 4, "cols_ctas_per_sm": 4, "cols_chunks": 0}
+    assert sorted(keys) == sorted(defaults), keys
+    lib = fdl.lib()
+    for key, value in defaults.items():
+        assert lib.fdl_set_tuning(key.encode(), value) == 0, key
+    assert lib.fdl_set_tuning(b"no_such_key", 1) != 0
+    assert lib.fdl_set_tuning(b"sum_cluster", 3) != 0
+    assert lib.fdl_set_tuning(b"rows_cluster_threads", 128) != 0
