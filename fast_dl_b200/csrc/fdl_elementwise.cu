@@ -11,6 +11,9 @@
 // index into operand offsets with multiply-high "fast division" constants that the host
 // derives from the collapsed shape, so the device never executes an integer divide
 // (the reference's row-bias kernel pays one `%` per element, src/kernels/cuda/bias.cu:10).
+// When the extents are not multiples of 4 but one operand has the output's own layout, a
+// second broadcast kernel walks that operand and the output as aligned packs of their flat
+// buffers and indexes only the other operand per element.
 #include "fdl_common.cuh"
 
 namespace fdl {

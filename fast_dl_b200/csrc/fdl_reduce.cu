@@ -6,6 +6,14 @@
 // memory -> distributed shared memory of a thread-block cluster -> (for grid-wide
 // results) per-cluster partials in scratch that the last cluster to finish folds in a
 // fixed order.  No floating-point atomics anywhere, so results are run-to-run identical.
+//
+// Which kernel a row reduction takes depends on the shape: rows of up to 256 floats go to
+// teams of lanes with several rows in flight, longer ones to a warp or a CTA per row, a few
+// very long rows are cut into segments (one CTA each, folded per row through scratch), and
+// rows at an arbitrary phase of a 16-byte line (odd lengths, unaligned bases) are walked
+// as aligned packs of the flat buffer with their two edge packs read float by float.
+// Column reductions have a tree-free form for up to 8 rows and own four columns per thread
+// (adjacent with 128-bit loads, a tile-width apart with 32-bit loads).
 #include <cooperative_groups.h>
 
 #include <cfloat>

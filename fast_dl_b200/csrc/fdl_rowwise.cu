@@ -1,8 +1,9 @@
 // Row softmax and row layernorm (fp32), one HBM read and one HBM write per element.
 //
 // A "team" of TPR threads owns a row and keeps it in registers (NV 128-bit packs per
-// thread): 8 or 16 lanes for very short rows, a warp up to 1024 floats, a whole CTA of 256
-// threads up to 8192 floats and of 512 threads up to 16384 floats.  Every CTA handles one
+// thread): 8 or 16 lanes for very short rows, a warp up to 1024 floats (up to 2048 where that
+// measured faster), a whole CTA of 256 threads up to 8192 floats and of 512 threads up to
+// 16384 floats.  Every CTA handles one
 // fixed group of rows and the hardware block scheduler spreads the CTAs over the SMs.
 //
 // Two ways of bringing a row in are built, selected by fdl_set_tuning("rows_staged", v):
@@ -20,9 +21,9 @@
 // 97-98%, so the default picks by row length.  Both forms stay selectable so the
 // comparison can be repeated on the same build.
 //
-// Rows of 16384 < cols <= 131072 floats are shared by a thread-block cluster of 2, 4 or 8
-// CTAs: each keeps a slice in registers and the row statistics cross the cluster through
-// distributed shared memory, so such a row is still read once and written once.
+// Rows of 16384 < cols <= 131072 floats are shared by a thread-block cluster of 4 or 8
+// CTAs: each keeps a slice in registers and the slice statistics cross the cluster once
+// through distributed shared memory, so such a row is still read once and written once.
 // Longer rows are cut into 32 KiB segments: one kernel leaves per-segment statistics and
 // combines them per row, a second applies them (two reads, one write).
 // Rows whose length is not a multiple of 4 floats, or whose base is not 16-byte aligned, take
