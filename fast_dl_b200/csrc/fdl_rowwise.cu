@@ -1186,7 +1186,7 @@ using namespace fdl;
 extern "C" {
 
 int fdl_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream) {
-    if (cols >= INT_MAX - 16) return FDL_ERR_UNSUPPORTED;  // pack arithmetic on a row stays inside int
+    if (cols >= INT_MAX - 16384) return FDL_ERR_UNSUPPORTED;  // pack and segment arithmetic on a row stays inside int
     RowParams p{};
     p.x = x;
     p.y = y;
@@ -1198,7 +1198,7 @@ int fdl_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, v
 int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float* y,
                            float* mean_out, float* rstd_out, int64_t rows, int64_t cols,
                            float eps, void* stream) {
-    if (cols >= INT_MAX - 16) return FDL_ERR_UNSUPPORTED;  // pack arithmetic on a row stays inside int
+    if (cols >= INT_MAX - 16384) return FDL_ERR_UNSUPPORTED;  // pack and segment arithmetic on a row stays inside int
     RowParams p{};
     p.x = x;
     p.y = y;
