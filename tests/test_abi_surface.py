@@ -1,6 +1,8 @@
 """The C-ABI library loads on a machine without a GPU and exports what the header declares."""
 import ctypes
 import re
+
+import pytest
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -62,3 +64,25 @@ def test_every_documented_tuning_key_is_accepted(fdl):
     assert lib.fdl_set_tuning(b"no_such_key", 1) != 0
     assert lib.fdl_set_tuning(b"sum_cluster", 3) != 0
     assert lib.fdl_set_tuning(b"rows_cluster_threads", 128) != 0
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own, and a C caller must
+    link against the library with nothing but the header (no C++ runtime symbols in the interface)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    header = ROOT / "include" / "fdl_kernels.h"
+    subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", str(header)],
+                   check=True)
+    src = tmp_path / "caller.c"
+    src.write_text('#include "fdl_kernels.h"\n#include <stdio.h>\n'
+                   'int main(void) { printf("%d %s\\n", fdl_version(), fdl_error_string(FDL_ERR_WORKSPACE)); return 0; }\n')
+    from fast_dl_b200 import build
+    lib = build.build_kernels()
+    exe = tmp_path / "caller"
+    subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe),
+                    "-L", str(lib.parent), "-lfdl_kernels", f"-Wl,-rpath,{lib.parent}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split(maxsplit=1)
+    assert int(out[0]) >= 1000 and "scratch" in out[1].lower()
