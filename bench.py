@@ -41,6 +41,16 @@ METRIC = "effective_GBps_large_tensor_sweep"
 WORKLOAD = "large_tensor_sweep_268435456_f32: z=x+y, w=x+row[1,16384], s=sum(x)"
 
 
+def workload_config(n_gpus: int, rows: int) -> dict:
+    """What is computed and how it is partitioned: the same dictionary in both arms."""
+    cfg = {"workload": WORKLOAD,
+           "partition": f"leading dimension ({rows} rows of 16384 floats) in contiguous blocks over {n_gpus} GPU(s)",
+           "l2": "inputs larger than L2"}
+    if rows != ROWS:
+        cfg["workload"] += f" (REDUCED to {rows} rows for a profiler capture; not a bench value)"
+    return cfg
+
+
 def algorithmic_bytes(rows: int, cols: int) -> dict:
     n = rows * cols
     return {"add": 12 * n, "broadcast_add": 8 * n + 4 * cols, "sum": 4 * n + 4}
@@ -210,7 +220,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "config": workload_config(args.gpus, ROWS),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -235,6 +245,8 @@ def traffic_per_launch(algorithmic: int):
 
 
 def run_ours(args) -> None:
+    import statistics
+
     import torch
     import torch.distributed as dist
     from fast_dl_b200 import capi
@@ -250,6 +262,9 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     capi.lib()
     capi.use_device(local)
+    for kv in args.tune:
+        key, val = kv.split("=")
+        capi.set_tuning(key, int(val))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
@@ -277,7 +292,6 @@ def run_ours(args) -> None:
             return handles
         exchange = capi.Exchange(world, rank, gather)
         dist.barrier()
-    d2, e2, row2 = d.view(rows, COLS), e.view(rows, COLS), row.view(1, COLS)
     stream = torch.cuda.current_stream().cuda_stream
     lib = capi.lib()
 
@@ -325,16 +339,22 @@ def run_ours(args) -> None:
     else:
         plan = [("add", op_add), ("broadcast_add", op_broadcast), ("sum", op_sum)]
     launches_per_step = len(plan)
+    fns = [fn for _, fn in plan]
+    nccl_sum = world > 1 and exchange is None
 
-    def step(events=None):
-        for i, (_, fn) in enumerate(plan):
-            if events is not None:
-                events[i].record()
+    def step():
+        for fn in fns:
             fn()
-        if events is not None:
-            events[len(plan)].record()
-        if world > 1 and exchange is None:
+        if nccl_sum:
             dist.all_reduce(sum64)  # per-GPU partials -> global sum: same stream, no host round trip
+
+    def step_with_events(events):
+        for i, fn in enumerate(fns):
+            events[i].record()
+            fn()
+        events[len(fns)].record()
+        if nccl_sum:
+            dist.all_reduce(sum64)
 
     def barrier():
         if world > 1:
@@ -346,11 +366,10 @@ def run_ours(args) -> None:
         step()
     barrier()
 
-    # ---- timed region: exactly K steps ---------------------------------------------------------
+    # ---- timed region: exactly K steps, launches back to back (no events between the ops) ----------
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(plan) + 1)] for _ in range(K)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, period_s=0.002)
     sampler.start()
     barrier()
     start.record()
@@ -361,45 +380,121 @@ def run_ours(args) -> None:
     for k in range(K):
         if k == k_host:
             enqueue_us = (time.perf_counter() - t_host) * 1e6 / k_host
-        step(ev[k])
+        step()
     stop.record()
     if K == k_host:
         enqueue_us = (time.perf_counter() - t_host) * 1e6 / k_host
     barrier()
     clocks = sampler.stop()
     ms_total = start.elapsed_time(stop)
-    per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K) for i, (name, _) in enumerate(plan)
-                  if name == which) / K for which in ("add", "broadcast_add", "sum")]
+
+    # ---- second pass, outside the headline: the same steps with an event between the ops -----------
+    K2 = max(3, min(K, 50))
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(plan) + 1)] for _ in range(K2)]
+    barrier()
+    for k in range(K2):
+        step_with_events(ev[k])
+    barrier()
+    per_op = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K2) for i, (name, _) in enumerate(plan)
+                  if name == which) / K2 for which in ("add", "broadcast_add", "sum")]
+
+    # ---- third pass: the same step for at least a second, with the clocks sampled under load ----
+    K3 = int(min(20000, max(K, args.sustain_s * 1e3 / max(ms_total / K, 1e-3))))
+    if world > 1:
+        k3 = torch.tensor([K3], dtype=torch.int64, device=dev)
+        dist.all_reduce(k3, op=dist.ReduceOp.MAX)
+        K3 = int(k3.item())
+    s_start, s_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler3 = ClockSampler(local, period_s=0.01)
+    sampler3.start()
+    barrier()
+    s_start.record()
+    for _ in range(K3):
+        step()
+    s_stop.record()
+    barrier()
+    clocks3 = sampler3.stop()
+    ms_sustained = s_start.elapsed_time(s_stop)
+
+    # ---- results of the last step, checked outside every timed region --------------------------------
+    step()
+    torch.cuda.synchronize()
+    check = {}
+    check["add"] = int((c.view(torch.int32) != (a + b).view(torch.int32)).sum().item())
+    check["broadcast"] = int((e.view(torch.int32) != (d.view(rows, COLS) + row).view(-1).view(torch.int32)).sum().item())
+    ref64 = f.double().sum().reshape(1)
+    sq = (f.double() * f.double()).sum().reshape(1)
+    if world > 1:
+        dist.all_reduce(ref64)
+        dist.all_reduce(sq)
+    norm = float(sq.sqrt().item())
+    got64, got32 = float(sum64.item()), float(sum32.item())
+    check["sum_rel"] = abs(got64 - float(ref64.item())) / max(abs(float(ref64.item())), norm)
+    check["sum_f32_rel"] = abs(got32 - float(ref64.item())) / max(abs(float(ref64.item())), norm)
+    agree = True
+    if world > 1:
+        mine = torch.cat([sum64.view(torch.int64), sum32.view(torch.int32).to(torch.int64)])
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        agree = all(bool(torch.equal(t, everyone[0])) for t in everyone)
+    check["ranks_agree"] = agree
+    bad = torch.tensor([check["add"], check["broadcast"], int(check["sum_rel"] > 1e-5), int(check["sum_f32_rel"] > 1e-5),
+                        int(not agree)], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(bad)  # a mismatch on any rank fails the run
+    check["add"], check["broadcast"] = int(bad[0].item()), int(bad[1].item())
+    check["what"] = ("differing elements of z = x + y and w = x + row against torch on the device (all ranks); the fp64 "
+                     "and fp32 full sums against an fp64 sum of the same data (NCCL all-reduce of the ranks' fp64 sums "
+                     "at N > 1), relative to max(|sum|, ||x||_2), allowed 1e-5; the result bits of all ranks compared")
+    check_failed = bool(bad.sum().item() != 0)
+    del ref64, sq
+
+    # ---- configuration 4 (row softmax / layernorm on [65536,1024]) sharded by rows over the ranks ----
+    del c, e, d, f, a, b
+    torch.cuda.empty_cache()
+    config4 = None
+    if not args.no_c4:
+        config4 = config4_per_op(capi, dist, dev, world, rank)
 
     # ---- end to end: host tensors in, host results out, through the C ABI ------------------------
     need_host = not args.no_e2e or (rank == 0 and world == 1 and not args.no_cpu)
     host = None
-    e2e_steps, e2e_sec, link_sec = 0, float("nan"), 0.0
+    e2e_steps, e2e_sec, e2e3_sec, link_sec = 0, float("nan"), 0.0, 0.0
     if need_host:
-        del c, e, d, f
-        torch.cuda.empty_cache()
         host = host_inputs(rows, 1000 + rank, pinned=True)
     if not args.no_e2e:
         hx, hy, hz, hw, hrow = host
         hx2, hy2, hz2, hw2 = (t.view(rows, COLS) for t in (hx, hy, hz, hw))
         tsum = torch.zeros(1, dtype=torch.float64, device=dev)
 
-        def e2e_step():
-            s = capi.host_sweep(hx2, hy2, hrow, hz2, hw2)
+        def finish_sum(s):
             if world > 1:
                 tsum.fill_(s)
                 dist.all_reduce(tsum)
                 s = float(tsum.item())
             return s
 
+        def e2e_step():
+            return finish_sum(capi.host_sweep(hx2, hy2, hrow, hz2, hw2))
+
+        def e2e_three_calls():
+            # The same three results from three separate calls: x crosses the link three times.
+            capi.host_binary(hx, hy, hz, ADD)
+            capi.host_row_broadcast(hx2, hrow, hw2, ADD)
+            return finish_sum(capi.host_sum(hx))
+
+        def time_host(fn, steps):
+            fn()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                fn()
+            barrier()
+            return (time.perf_counter() - t0) / steps
+
         e2e_steps = max(2, min(5, K))
-        e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        barrier()
-        e2e_sec = (time.perf_counter() - t0) / e2e_steps
+        e2e_sec = time_host(e2e_step, e2e_steps)
+        e2e3_sec = time_host(e2e_three_calls, 2)
 
         # What the host link itself gives on this box, for the e2e figure to be read against:
         # x up and z down as two plain pinned copies running at the same time (all ranks at once).
@@ -423,11 +518,11 @@ def run_ours(args) -> None:
         del up_dst, down_src
 
     # ---- reduce over ranks: the slowest rank defines the time --------------------------------------
-    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op, enqueue_us, link_sec],
-                         dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms_total, e2e_sec if e2e_steps else 0.0, *per_op, enqueue_us, link_sec, ms_sustained,
+                          e2e3_sec], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms_total, e2e_sec, t_add, t_bc, t_sum, enqueue_us, link_sec = stats.tolist()
+    ms_total, e2e_sec, t_add, t_bc, t_sum, enqueue_us, link_sec, ms_sustained, e2e3_sec = stats.tolist()
 
     total_bytes = sum(algorithmic_bytes(args.rows, COLS).values()) + (world - 1) * (4 * COLS + 4)
     value = total_bytes * K / (ms_total * 1e-3) / 1e9
@@ -443,19 +538,18 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": warmup,
         "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD,
-                   "partition": f"leading dimension over {world} GPU(s): {rows} of {args.rows} rows on rank 0",
-                   "l2": "inputs larger than L2 (six distinct tensors stream per step)",
-                   "full_sum_exchange": ("none (1 GPU)" if world == 1 else
-                                         "split: the sum kernel sends the partial over NVLink (peer stores), the "
-                                         "other two ops overlap the exchange, a one-warp kernel folds" if split else
-                                         "fused into the sum kernel (peer stores over NVLink)" if exchange is not None
-                                         else "NCCL all-reduce of one double")},
+        "config": workload_config(world, args.rows),
         "clocks": clocks,
+        "check": check,
         "e2e": {"value": (total_bytes / e2e_sec / 1e9) if e2e_steps else None, "unit": "GB/s",
                 "h2d_bytes_per_step": (2 * args.rows * COLS + world * COLS) * 4,
                 "d2h_bytes_per_step": 2 * args.rows * COLS * 4 + 8 * world, "steps": e2e_steps,
                 "api": "fdl_host_sweep_f32 (pinned host tensors in, host results out)",
+                "three_separate_calls": (None if not e2e3_sec else {
+                    "value": total_bytes / e2e3_sec / 1e9, "unit": "GB/s",
+                    "api": "fdl_host_binary_f32 + fdl_host_row_broadcast_f32 + fdl_host_sum_f32",
+                    "h2d_bytes_per_step": (4 * args.rows * COLS + world * COLS) * 4,
+                    "d2h_bytes_per_step": 2 * args.rows * COLS * 4 + 8 * world}),
                 # e2e moves 2 tensors up and 2 down per step; the link line is one up + one down at once
                 "link": (None if not link_sec else {
                     "duplex_GBps_per_direction": args.rows * COLS * 4 / link_sec / 1e9,
@@ -466,12 +560,23 @@ def run_ours(args) -> None:
         "host_enqueue_us_per_step": enqueue_us,
         "roofline": {"bound": "hbm", "kernel": "map_kernel<4,2,4,AddFn> (binary add)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "traffic": traffic_per_launch(big["add"])},
+                     "traffic": traffic_per_launch(big["add"]),
+                     "timed": f"events around each launch in a second pass of {K2} steps (not in the headline region)"},
         "per_op": {"add": op_line("add", t_add), "broadcast_add": op_line("broadcast_add", t_bc),
                    "sum": op_line("sum", t_sum)},
+        "sustained": {"value": total_bytes * K3 / (ms_sustained * 1e-3) / 1e9, "unit": "GB/s", "steps": K3,
+                      "seconds": ms_sustained * 1e-3, "ms_per_step": ms_sustained / K3, "clocks": clocks3},
+        "implementation": {
+            "tensors": "six distinct device tensors stream per step",
+            "full_sum_exchange": ("none (1 GPU)" if world == 1 else
+                                  "split: the sum kernel sends the partial over NVLink (peer stores), the "
+                                  "other two ops overlap the exchange, a one-warp kernel folds" if split else
+                                  "fused into the sum kernel (peer stores over NVLink)" if exchange is not None
+                                  else "NCCL all-reduce of one double"),
+            "tuning": args.tune},
     }
-    if args.rows != ROWS:
-        line["config"]["workload"] += f" (REDUCED to {args.rows} rows for a profiler capture; not a bench value)"
+    if config4 is not None:
+        line["config4_per_op"] = config4
 
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
@@ -495,6 +600,60 @@ def run_ours(args) -> None:
         if exchange is not None:
             exchange.close()
         dist.destroy_process_group()
+    if check_failed:
+        raise SystemExit(f"result check failed: {check}")
+
+
+def config4_per_op(capi, dist, dev, world: int, rank: int, iters: int = 10) -> dict:
+    """Row softmax and layernorm on logits[65536,1024], sharded by rows over the ranks: each rank
+    times its shard (CUDA events around one launch, L2 flushed by reading 512 MiB before it,
+    median of `iters`), the slowest rank defines the time, GB/s is whole-tensor bytes over it."""
+    import statistics
+
+    import torch
+    from fast_dl_b200.sharding import shard_rows
+
+    R, Ccols = 65536, 1024
+    r = shard_rows(R, world, rank).count
+    gen = torch.Generator(device=dev).manual_seed(4242 + rank)
+    logits = torch.empty((r, Ccols), dtype=torch.float32, device=dev).normal_(0.0, 3.0, generator=gen)
+    gamma = torch.empty(Ccols, dtype=torch.float32, device=dev).uniform_(0.9, 1.1, generator=gen)
+    beta = torch.empty(Ccols, dtype=torch.float32, device=dev).uniform_(-0.1, 0.1, generator=gen)
+    out = torch.empty_like(logits)
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    peak, _ = measured_peak_gbs()
+    ops = {
+        "softmax": (8 * R * Ccols, lambda: capi.softmax_rows(logits, out=out)),
+        "layernorm": (8 * R * Ccols, lambda: capi.layernorm_rows(logits, out=out)),
+        "layernorm_gamma_beta": (8 * R * Ccols + 8 * Ccols * world, lambda: capi.layernorm_rows(logits, gamma, beta, out=out)),
+    }
+    res = {"shape": [R, Ccols], "rows_per_gpu": r, "method": "per-launch CUDA events, read-flushed L2, median, max over ranks"}
+    for name, (nbytes, fn) in ops.items():
+        times = []
+        for i in range(iters + 3):
+            if world > 1:
+                dist.barrier()
+            capi.full_sum(flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        res[name] = {"ms": ms, "GBps": nbytes / ms / 1e6, "frac_per_gpu": nbytes / ms / 1e6 / (world * peak)}
+    # correctness of the shard-local results: rows sum to one; layernorm rows have mean 0, variance 1
+    capi.softmax_rows(logits, out=out)
+    res["softmax_row_sum_err"] = float((out.double().sum(dim=1) - 1.0).abs().max().item())
+    capi.layernorm_rows(logits, out=out)
+    res["layernorm_row_mean_abs"] = float(out.double().mean(dim=1).abs().max().item())
+    del logits, out, flush
+    torch.cuda.empty_cache()
+    return res
 
 
 def main() -> None:
@@ -509,6 +668,10 @@ def main() -> None:
                          "(split), or with a separate NCCL all-reduce (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-c4", action="store_true", help="skip the per-op figures of configuration 4")
+    ap.add_argument("--sustain-s", type=float, default=1.0,
+                    help="length in seconds of the extra pass that repeats the step with the clocks sampled")
+    ap.add_argument("--tune", action="append", default=[], help="key=value passed to fdl_set_tuning")
     ap.add_argument("--rows", type=int, default=ROWS,
                     help="rows of the [rows, 16384] view; smaller than 16384 only for profiler captures")
     args = ap.parse_args()

@@ -1,17 +1,29 @@
 // dl::kernels -- the reference's kernel-level functions as forwards into the C ABI.
+//
+// This file defines exactly the functions that fast_dl's include/dl/kernels/*.hpp declare and
+// depends on nothing else of the host library, so the same source compiles against
+// fast_dl's own headers: there it is the "forwarding source" that replaces the seven
+// hot-path .cu files of dl_cuda_kernels behind an unmodified dl_core (CMakeLists.txt:44-56, 75).
+// A signature that drifts from the reference's header is then a compile or link error.
+// Functions this library adds to the namespace live in kernels_ext.cpp.
 #include <dl/kernels/kernels.hpp>
-
-#include <dl/core/CudaUtils.hpp>
 
 #include <fdl_kernels.h>
 
 #include <stdexcept>
+#include <string>
 
 namespace dl::kernels {
 
 namespace {
-using dl::cuda::check_fdl;
 constexpr void* kLegacyStream = nullptr;  // what the reference launches on
+
+// The reference's kernel functions return void and its callers ask cudaGetLastError; a
+// failure reported by the C ABI surfaces as std::runtime_error("<action>: <text>"), the
+// form of dl::cuda::check (src/core/CudaUtils.cpp:8-13).
+void check_fdl(int status, const char* action) {
+    if (status != FDL_OK) throw std::runtime_error(std::string(action) + ": " + fdl_error_string(status));
+}
 }  // namespace
 
 const char* to_string(ElementwiseOp op) {
@@ -62,10 +74,6 @@ void add_row_bias(float* output, const float* bias, int rows, int cols) {
     check_fdl(fdl_add_row_bias_f32(output, bias, rows, cols, kLegacyStream), "add_row_bias kernel");
 }
 
-void add_row_bias_relu(float* output, const float* bias, int rows, int cols) {
-    check_fdl(fdl_add_row_bias_relu_f32(output, bias, rows, cols, kLegacyStream), "add_row_bias_relu kernel");
-}
-
 void reduction(const float* input, float* output, std::size_t size, ReductionAlgo algo) {
     check_fdl(fdl_block_reduce_1024_f32(input, output, static_cast<int64_t>(size), static_cast<int>(algo),
                                         kLegacyStream),
@@ -79,18 +87,9 @@ void softmax(const float* input, float* output, std::size_t rows, std::size_t co
 }
 
 void layernorm(const float* input, float* output, int rows, int cols, float eps) {
-    layernorm_affine(input, nullptr, nullptr, output, rows, cols, eps);
-}
-
-void layernorm_affine(const float* input, const float* gamma, const float* beta, float* output, int rows,
-                      int cols, float eps) {
-    check_fdl(fdl_layernorm_rows_f32(input, gamma, beta, output, nullptr, nullptr, rows, cols, eps,
+    check_fdl(fdl_layernorm_rows_f32(input, nullptr, nullptr, output, nullptr, nullptr, rows, cols, eps,
                                      kLegacyStream),
               "layernorm kernel");
-}
-
-void mul_add_relu(const float* a, const float* b, const float* c, float* out, int64_t n) {
-    check_fdl(fdl_mul_add_relu_f32(a, b, c, out, n, kLegacyStream), "mul_add_relu kernel");
 }
 
 void cross_entropy(const float* logits, const int64_t* labels, float* loss, int batch, int classes) {

@@ -22,6 +22,18 @@ Outputs
   oracle/_ref/tests/<name>    - the reference's own test programs (tests/tensor, tests/nn)
                                 compiled UNMODIFIED against this repository's dl:: headers and
                                 linked with libdl_core.so / libfdl_kernels.so.
+  oracle/_ref/libdl_core_reference.so
+                              - the reference's link line (CMakeLists.txt:24-56, 75) with the
+                                kernel library swapped: its UNMODIFIED src/core, src/tensor,
+                                src/ops and src/nn sources compiled against its own include/,
+                                plus this repository's forwarding source
+                                (fast_dl_b200/host/src/kernels_shim.cpp and gemm.cpp, compiled
+                                against the reference's include/dl/kernels/*.hpp) in place of
+                                dl_cuda_kernels, linked with libfdl_kernels.so.
+  oracle/_ref/tests_refcore/<name>
+                              - the same 17 test programs compiled against the reference's
+                                headers and linked with that library: the replacement kernel
+                                library behind the reference's own host code.
 """
 from __future__ import annotations
 
@@ -117,11 +129,65 @@ def build_tests(force: bool = False) -> list[Path]:
     return built
 
 
+REF_CORE_DIRS = ["core", "tensor", "ops", "nn"]
+
+
+def refcore_lib_path() -> Path:
+    return OUT / "libdl_core_reference.so"
+
+
+def build_refcore(force: bool = False) -> list[Path]:
+    """The reference's own dl_core on top of libfdl_kernels.so, and its 17 tests against it."""
+    libdir = ROOT / "fast_dl_b200" / "lib"
+    kernels = libdir / "libfdl_kernels.so"
+    outdir = OUT / "tests_refcore"
+    if not reference_available() or not kernels.exists():
+        return sorted(outdir.glob("*")) if outdir.exists() else []
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cuda_home = Path(nvcc).resolve().parent.parent
+    objdir = OUT / "obj_refcore"
+    objdir.mkdir(parents=True, exist_ok=True)
+    outdir.mkdir(parents=True, exist_ok=True)
+    host_src = ROOT / "fast_dl_b200" / "host" / "src"
+    # The include directories of the reference's dl_core target (CMakeLists.txt:59-67).
+    ref_inc = [REF / "include", REF / "include" / "dl"] + [REF / "include" / "dl" / d for d in
+                                                        ("core", "kernels", "ops", "tensor")]
+    inc = [a for d in ref_inc for a in ("-I", d)] + ["-I", cuda_home / "include"]
+    sources = [p for d in REF_CORE_DIRS for p in sorted((REF / "src" / d).glob("*.cpp"))]
+    forwards = [host_src / "kernels_shim.cpp", host_src / "gemm.cpp"]
+    lib = refcore_lib_path()
+    stamp = max(p.stat().st_mtime for p in forwards + [kernels])
+    if force or not lib.exists() or lib.stat().st_mtime < stamp:
+        objects = []
+        for src in sources:
+            obj = objdir / f"ref_{src.parent.name}_{src.stem}.o"
+            _run(["g++", "-O2", "-std=c++17", "-fPIC", *inc, "-c", src, "-o", obj])
+            objects.append(obj)
+        for src in forwards:  # against the REFERENCE's kernel headers, plus the C ABI header
+            obj = objdir / f"fwd_{src.stem}.o"
+            _run(["g++", "-O2", "-std=c++17", "-fPIC", "-Wall", "-Wextra", *inc, "-I", ROOT / "include",
+                  "-c", src, "-o", obj])
+            objects.append(obj)
+        _run(["g++", "-shared", "-o", lib, *objects, "-L", libdir, "-lfdl_kernels",
+              "-Wl,-rpath,$ORIGIN/../../fast_dl_b200/lib", "-L", cuda_home / "lib64", "-lcudart", "-lcublas"])
+    built = []
+    for rel in REF_TESTS:
+        src = REF / "tests" / (rel + ".cpp")
+        exe = outdir / Path(rel).name
+        if force or not exe.exists() or exe.stat().st_mtime < lib.stat().st_mtime:
+            _run(["g++", "-O1", "-std=c++17", *inc, src, "-o", exe, "-L", OUT, "-ldl_core_reference",
+                  "-L", libdir, "-lfdl_kernels", "-L", cuda_home / "lib64", "-lcudart",
+                  "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath,$ORIGIN/../../../fast_dl_b200/lib"])
+        built.append(exe)
+    return built
+
+
 def build(force: bool = False):
-    return build_lib(force), build_tests(force)
+    return build_lib(force), build_tests(force), build_refcore(force)
 
 
 if __name__ == "__main__":
-    lib, tests = build(force=True)
+    lib, tests, refcore_tests = build(force=True)
     print(lib)
-    print(len(tests), "reference test programs")
+    print(len(tests), "reference test programs against this repository's host library")
+    print(len(refcore_tests), "reference test programs against the reference's own host library + libfdl_kernels.so")
