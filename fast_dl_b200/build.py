@@ -27,7 +27,10 @@ LIB = PKG / "lib"
 HOST = PKG / "host"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# Hidden visibility: the header marks the extern "C" entry points default-visible when
+# FDL_BUILDING_LIBRARY is defined, so the library exports the C ABI and nothing else.
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+              "-DFDL_BUILDING_LIBRARY"]
 
 
 def _nvcc() -> str:

@@ -30,6 +30,7 @@ PROTOTYPES = {
     "fdl_stream_synchronize": (_int, [_vp]),
     "fdl_take_device_error": (_int, []),
     "fdl_set_tuning": (_int, [C.c_char_p, _int]),
+    "fdl_debug_sum_trace": (_int, [C.POINTER(C.c_uint64)]),
     "fdl_binary_f32": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
     "fdl_unary_f32": (_int, [_vp, _vp, _i64, _int, _f32, _vp]),
     "fdl_mul_add_relu_f32": (_int, [_vp, _vp, _vp, _vp, _i64, _vp]),
@@ -44,6 +45,8 @@ PROTOTYPES = {
     "fdl_exchange_create": (_int, [_int, _int, C.POINTER(C.c_void_p)]),
     "fdl_exchange_local_handle": (_int, [_vp, C.c_char_p]),
     "fdl_exchange_connect": (_int, [_vp, C.c_char_p]),
+    "fdl_exchange_buffer": (_int, [_vp, C.POINTER(C.c_void_p)]),
+    "fdl_exchange_connect_pointers": (_int, [_vp, C.POINTER(C.c_void_p)]),
     "fdl_exchange_destroy": (_int, [_vp]),
     "fdl_sum_allreduce_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fdl_sum_allreduce_start_f32": (_int, [_vp, _i64, _vp, _vp, _sz, _vp]),
@@ -319,6 +322,13 @@ def random_fill(n, normal, p0, p1, seed, device="cuda"):
     fn = lib().fdl_normal_f32 if normal else lib().fdl_uniform_f32
     check(fn(_ptr(out), n, p0, p1, seed, _stream()), "fdl_random_fill")
     return out
+
+
+def sum_trace() -> list:
+    """The eight words left by the most recent full sum launched with the tuning key sum_trace set."""
+    words = (C.c_uint64 * 8)()
+    check(lib().fdl_debug_sum_trace(words), "fdl_debug_sum_trace")
+    return list(words)
 
 
 def take_device_error() -> None:

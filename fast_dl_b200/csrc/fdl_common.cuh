@@ -53,6 +53,12 @@ struct Tuning {
                                  // lane (1), by a 256-thread CTA (0), or whichever measured faster (-1)
     int rows_staged = -1;  // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA,
                            // -1 = staged for rows of up to 128 floats, direct beyond
+    int pdl = 1;           // streaming kernels are launched with programmatic stream serialization: the
+                           // next kernel's launch and ramp-up overlap this one's tail (0 = plain launches)
+    int exchange_wait_ms = 2000;  // how long a cross-GPU exchange waits for its peers before giving up
+    int sum_trace = 0;     // 1: the full sum's finishing CTA leaves %globaltimer stamps (fdl_debug_sum_trace)
+    int bcast2d = 1;       // two-dimensional broadcasts take the division-free kernel (0 = the general one)
+    int bcast2d_rows = 0;  // rows per thread in that kernel: 1, 2 or 4 (0 = by size)
 };
 Tuning& tuning();
 
@@ -65,8 +71,45 @@ constexpr int kWorkspaceCounterBytes = 65536;
 
 // One word of host-mapped pinned memory per process in which kernels raise bits when a
 // bounded device-side wait runs out (bit 0: bulk-copy wait, bit 1: cross-GPU exchange wait).
+// The same 256-byte block carries, from byte 64 on, eight 64-bit time stamps that the full
+// sum's finishing CTA writes when tuning().sum_trace is set.
 int error_flag_device_ptr(unsigned int** dev);
 unsigned int read_and_clear_device_error_flag();
+constexpr int kTraceWords = 8;
+const unsigned long long* trace_words_host();
+
+// Launch with optional thread-block clusters along x (or y) and optional programmatic
+// stream serialization.  With `pdl`, the kernel may be scheduled while the previous kernel
+// of the stream is still draining; it must execute pdl_wait() before its first global
+// access, which every kernel launched through here does.
+template <class... KArgs, class... Args>
+int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+              dim3 cluster, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned int n = 0;
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = cluster.x;
+        attrs[n].val.clusterDim.y = cluster.y;
+        attrs[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    if (pdl) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return static_cast<int>(cudaGetLastError());
+}
 
 // Persistent-grid size: enough blocks to fill every SM `blocks_per_sm` times, but never
 // more than the work needs.
@@ -79,6 +122,13 @@ inline int persistent_grid(const DeviceInfo* info, int blocks_per_sm, int64_t wo
 // ---- device side -----------------------------------------------------------------------
 
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  pdl_wait(): returns once the previous kernel of the stream
+// has completed and its writes are visible (a no-op for a kernel launched the plain way).
+// pdl_trigger(): this CTA no longer delays the launch of the next kernel; that kernel's
+// own pdl_wait() still waits for the whole of this grid.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Streaming (evict-first) 128-bit accesses: every byte on this path is touched once.
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }

@@ -142,6 +142,7 @@ map_kernel(F f, const float* in0, const float* in1, const float* in2, float* out
            int64_t n) {
     constexpr int64_t kTile = static_cast<int64_t>(kEwThreads) * kEwUnroll;
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile + threadIdx.x;
+    pdl_wait();  // the operands may be the previous kernel's output
     if (base + (kEwUnroll - 1) * kEwThreads < npack) {
         // Full tile (all CTAs but possibly the last): every load is issued before any use.
         Pack<W> x0[kEwUnroll], x1[kEwUnroll], x2[kEwUnroll];
@@ -152,6 +153,7 @@ map_kernel(F f, const float* in0, const float* in1, const float* in2, float* out
             if (NIN > 1) x1[u] = load_pack<W>(in1, i);
             if (NIN > 2) x2[u] = load_pack<W>(in2, i);
         }
+        pdl_trigger();  // loads are in flight: the next kernel of the stream may be scheduled
 #pragma unroll
         for (int u = 0; u < kEwUnroll; ++u) {
             const int64_t i = base + u * kEwThreads;
@@ -195,10 +197,9 @@ int launch_map_wu(const F& f, const float* in0, const float* in1, const float* i
         const int64_t npack = m / W;
         int64_t tiles = ceil_div(npack, kTile);
         if (tiles < 1) tiles = 1;
-        map_kernel<W, NIN, U, F><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(
-            f, in0 + off, NIN > 1 ? in1 + off : nullptr, NIN > 2 ? in2 + off : nullptr, out + off,
-            npack, m);
-        const int st = launch_status();
+        const int st = launch_ex(map_kernel<W, NIN, U, F>, dim3(static_cast<unsigned int>(tiles)), dim3(kEwThreads),
+                                 0, stream, dim3(1, 1, 1), tuning().pdl != 0, f, in0 + off,
+                                 NIN > 1 ? in1 + off : nullptr, NIN > 2 ? in2 + off : nullptr, out + off, npack, m);
         if (st != FDL_OK) return st;
     }
     return FDL_OK;
@@ -302,6 +303,7 @@ broadcast_kernel(F f, const __grid_constant__ BroadcastPlan plan, const float* a
     const uint32_t total = plan.total_packs;
     const uint32_t base = blockIdx.x * kTile + threadIdx.x;
     Pack<W> xa[kEwUnroll], xb[kEwUnroll];
+    pdl_wait();
 #pragma unroll
     for (int u = 0; u < kEwUnroll; ++u) {
         const uint32_t item = base + u * kEwThreads;
@@ -312,10 +314,113 @@ broadcast_kernel(F f, const __grid_constant__ BroadcastPlan plan, const float* a
             xb[u] = load_operand<W>(b, bo, plan.b_inner);
         }
     }
+    pdl_trigger();
 #pragma unroll
     for (int u = 0; u < kEwUnroll; ++u) {
         const uint32_t item = base + u * kEwThreads;
         if (item < total) store_pack<W>(out, item, apply<W>(f, xa[u], xb[u], xa[u]));
+    }
+}
+
+// ---- two collapsed dimensions: no index arithmetic at all -----------------------------------------
+//
+// [R, C] against [1, C], [R, 1] or another [R, C] with its own row stride -- the bias row, the
+// per-row scale, the view of a wider matrix.  Threads are laid out TX across the packs of a
+// row and 256 / TX down the rows; a thread walks ROWS rows at one pack position, so a row
+// vector's pack is loaded once per thread and a column vector's value once per row, both
+// through the read-only path (they are re-read by every CTA), while the dense operand and
+// the output stream past with evict-first accesses.  Consecutive CTAs take consecutive column
+// tiles of the same rows.  Operand kinds: 0 = one 128-bit load per row (inner stride 1, any
+// row stride that keeps 16-byte alignment), 1 = a row vector (inner stride 1, row stride 0),
+// 2 = one value per row (inner stride 0).
+template <class F, int KA, int KB, int ROWS>
+__global__ void __launch_bounds__(kEwThreads)
+broadcast2d_kernel(F f, const float* a, const float* b, float* out, int64_t rows, int64_t cpacks,
+                   int64_t a_rs, int64_t b_rs, int tx_shift, uint32_t col_tiles) {
+    const int tx = 1 << tx_shift;
+    const int ty = kEwThreads >> tx_shift;
+    const int cx = threadIdx.x & (tx - 1);
+    const int ry = threadIdx.x >> tx_shift;
+    const uint32_t row_group = blockIdx.x / col_tiles;
+    const uint32_t col_tile = blockIdx.x - row_group * col_tiles;
+    const int64_t cp = static_cast<int64_t>(col_tile) * tx + cx;
+    const int64_t r0 = static_cast<int64_t>(row_group) * (ty * ROWS) + ry;
+    pdl_wait();
+    if (cp >= cpacks) return;
+    Pack<4> xa[ROWS], xb[ROWS];
+    if (KA == 1) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(a) + cp);
+        xa[0] = Pack<4>{{t.x, t.y, t.z, t.w}};
+    }
+    if (KB == 1) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(b) + cp);
+        xb[0] = Pack<4>{{t.x, t.y, t.z, t.w}};
+    }
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+        const int64_t r = r0 + u * ty;
+        if (r < rows) {
+            if (KA == 0) xa[u] = load_pack<4>(a + r * a_rs, cp);
+            if (KA == 1) xa[u] = xa[0];
+            if (KA == 2) xa[u] = splat<4>(__ldg(a + r * a_rs));
+            if (KB == 0) xb[u] = load_pack<4>(b + r * b_rs, cp);
+            if (KB == 1) xb[u] = xb[0];
+            if (KB == 2) xb[u] = splat<4>(__ldg(b + r * b_rs));
+        }
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+        const int64_t r = r0 + u * ty;
+        if (r < rows) store_pack<4>(out + r * cpacks * 4, cp, apply<4>(f, xa[u], xb[u], xa[u]));
+    }
+}
+
+inline int operand_kind(int64_t row_stride, int64_t inner_stride) {
+    return inner_stride == 0 ? 2 : (row_stride == 0 ? 1 : 0);
+}
+
+template <class F, int ROWS>
+int launch_broadcast2d_rows(const F& f, const float* a, const float* b, float* out, int64_t rows, int64_t cols,
+                            int64_t a_rs, int64_t a_cs, int64_t b_rs, int64_t b_cs, cudaStream_t stream) {
+    const int64_t cpacks = cols / 4;
+    int tx_shift = 0;
+    while ((1 << tx_shift) < kEwThreads && (int64_t{1} << tx_shift) < cpacks) ++tx_shift;
+    const int tx = 1 << tx_shift, ty = kEwThreads >> tx_shift;
+    const int64_t col_tiles = ceil_div(cpacks, tx);
+    const int64_t row_groups = ceil_div(rows, static_cast<int64_t>(ty) * ROWS);
+    if (col_tiles * row_groups > kMaxGrid) return FDL_ERR_UNSUPPORTED;
+    const dim3 grid(static_cast<unsigned int>(col_tiles * row_groups)), block(kEwThreads), one(1, 1, 1);
+    const bool pdl = tuning().pdl != 0;
+    const uint32_t ct = static_cast<uint32_t>(col_tiles);
+#define FDL_B2D(KA, KB) \
+    return launch_ex(broadcast2d_kernel<F, KA, KB, ROWS>, grid, block, 0, stream, one, pdl, f, a, b, out, rows, cpacks, \
+                     a_rs, b_rs, tx_shift, ct)
+    switch (operand_kind(a_rs, a_cs) * 3 + operand_kind(b_rs, b_cs)) {
+        case 0: FDL_B2D(0, 0);
+        case 1: FDL_B2D(0, 1);
+        case 2: FDL_B2D(0, 2);
+        case 3: FDL_B2D(1, 0);
+        case 4: FDL_B2D(1, 1);
+        case 5: FDL_B2D(1, 2);
+        case 6: FDL_B2D(2, 0);
+        case 7: FDL_B2D(2, 1);
+        default: FDL_B2D(2, 2);
+    }
+#undef FDL_B2D
+}
+
+template <class F>
+int launch_broadcast2d(const F& f, const float* a, const float* b, float* out, int64_t rows, int64_t cols,
+                       int64_t a_rs, int64_t a_cs, int64_t b_rs, int64_t b_cs, cudaStream_t stream) {
+    // Rows per thread: four 128-bit loads in flight per dense operand once the tensor is large
+    // enough to fill every SM several times over, fewer below so that the last wave stays short.
+    int rows_per_thread = tuning().bcast2d_rows;
+    if (rows_per_thread == 0) rows_per_thread = rows * cols < (int64_t{1} << 22) ? 1 : 4;
+    switch (rows_per_thread) {
+        case 1: return launch_broadcast2d_rows<F, 1>(f, a, b, out, rows, cols, a_rs, a_cs, b_rs, b_cs, stream);
+        case 2: return launch_broadcast2d_rows<F, 2>(f, a, b, out, rows, cols, a_rs, a_cs, b_rs, b_cs, stream);
+        default: return launch_broadcast2d_rows<F, 4>(f, a, b, out, rows, cols, a_rs, a_cs, b_rs, b_cs, stream);
     }
 }
 
@@ -336,6 +441,7 @@ broadcast_flat_kernel(F f, const __grid_constant__ BroadcastPlan plan, const flo
     const uint32_t base = blockIdx.x * kTile + threadIdx.x;
     const int64_t other_inner = DENSE_IS_A ? plan.b_inner : plan.a_inner;
     Pack<4> xd[kEwUnroll], xo[kEwUnroll];
+    pdl_wait();
 #pragma unroll
     for (int u = 0; u < kEwUnroll; ++u) {
         const uint32_t item = base + u * kEwThreads;
@@ -402,20 +508,18 @@ int launch_broadcast_flat(const F& f, const BroadcastPlan& plan, bool dense_is_a
                           const float* other, float* out, uint32_t n, cudaStream_t stream) {
     int64_t tiles = ceil_div(static_cast<int64_t>(n >> 2), static_cast<int64_t>(kEwThreads) * kEwUnroll);
     if (tiles < 1) tiles = 1;
-    if (dense_is_a) {
-        broadcast_flat_kernel<F, true><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(f, plan, dense, other, out, n);
-    } else {
-        broadcast_flat_kernel<F, false><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(f, plan, dense, other, out, n);
-    }
-    return launch_status();
+    const dim3 grid(static_cast<unsigned int>(tiles)), block(kEwThreads), one(1, 1, 1);
+    const bool pdl = tuning().pdl != 0;
+    return dense_is_a ? launch_ex(broadcast_flat_kernel<F, true>, grid, block, 0, stream, one, pdl, f, plan, dense, other, out, n)
+                      : launch_ex(broadcast_flat_kernel<F, false>, grid, block, 0, stream, one, pdl, f, plan, dense, other, out, n);
 }
 
 template <int W, class F>
 int launch_broadcast_w(const F& f, const BroadcastPlan& plan, const float* a, const float* b,
                        float* out, cudaStream_t stream) {
     const int64_t tiles = ceil_div(plan.total_packs, kEwThreads * kEwUnroll);
-    broadcast_kernel<W, F><<<static_cast<unsigned int>(tiles), kEwThreads, 0, stream>>>(f, plan, a, b, out);
-    return launch_status();
+    return launch_ex(broadcast_kernel<W, F>, dim3(static_cast<unsigned int>(tiles)), dim3(kEwThreads), 0, stream,
+                     dim3(1, 1, 1), tuning().pdl != 0, f, plan, a, b, out);
 }
 
 struct Dim {
@@ -482,6 +586,11 @@ int run_broadcast(const F& f, const float* a, const float* b, float* out, int nd
     for (int i = 0; i + 1 < nd && vec; ++i) {
         if (inner.a == 1 && dims[i].a % 4 != 0) vec = false;
         if (inner.b == 1 && dims[i].b % 4 != 0) vec = false;
+    }
+    if (vec && nd == 2 && tuning().bcast2d != 0 && dims[0].size < (int64_t{1} << 31)) {
+        const int st = launch_broadcast2d<F>(f, a, b, out, dims[0].size, inner.size, dims[0].a, inner.a, dims[0].b,
+                                             inner.b, stream);
+        if (st != FDL_ERR_UNSUPPORTED) return st;
     }
     const int w = vec ? 4 : 1;
     const int64_t inner_packs = inner.size / w;

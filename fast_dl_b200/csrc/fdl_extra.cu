@@ -16,36 +16,157 @@ __device__ __forceinline__ bool aligned16_dev(const void* p) {
 
 // ---- cross-entropy ------------------------------------------------------------------------------
 //
-// The reference walks each row with ONE thread and adds loss_i / batch into a single float
-// with atomicAdd (src/kernels/cuda/cross_entropy.cu:9-35): uncoalesced and order-dependent.
-// Here a warp owns a row (coalesced 128-bit loads when possible), writes loss_i / batch to a
-// scratch vector, and the deterministic full sum folds that vector.  Rows whose label is
-// out of range contribute 0, as in the reference (:17-19).
+// The reference walks each row with ONE thread, twice, and adds loss_i / batch into a single
+// float with atomicAdd (src/kernels/cuda/cross_entropy.cu:9-35): uncoalesced, two reads and
+// order-dependent.  Here a team of TPR lanes owns a row and reads it ONCE with 128-bit loads,
+// eight per lane in flight: every lane keeps a running (max, sum of exp) pair that is
+// rescaled when the maximum moves (the row statistics of softmax, computed online), the
+// pairs meet through shuffles, and lane 0 forms log(sum) + max - x[label].  Rows whose label
+// is out of range contribute 0, as in the reference (:17-19).  The batch mean is
+// deterministic: loss_i / batch goes to a scratch vector and the full sum (launched so that
+// its start overlaps this kernel's tail) folds that vector in a fixed order.  A form that
+// folded inside this kernel (a double per CTA, a ticket, the last CTA adding them) measured
+// 51 us on [65536, 1024] against the 41 us of its traffic: the fence and the ticket's round
+// trip keep every CTA resident for a microsecond in which it has no loads in flight.
 
 constexpr int kCeThreads = 256;
+constexpr int kCeInFlight = 8;  // items (128-bit packs, or floats) a lane loads before it uses them
+constexpr float kLog2e = 1.4426950408889634f;
 
-__global__ void __launch_bounds__(kCeThreads)
-cross_entropy_rows_kernel(const float* logits, const int64_t* labels, float* row_loss, int batch,
-                          int classes, float inv_batch) {
-    const int lane = threadIdx.x & (kWarp - 1);
-    const int row = blockIdx.x * (kCeThreads / kWarp) + threadIdx.x / kWarp;
-    if (row >= batch) return;
-    const int64_t label = labels[row];
-    if (label < 0 || label >= classes) {
-        if (lane == 0) row_loss[row] = 0.0f;
-        return;
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// exp(a - b) for a <= b; 1 when both are -inf (a lane that has seen nothing yet).
+__device__ __forceinline__ float exp_diff(float a, float b) {
+    return a == b ? 1.0f : exp2_approx((a - b) * kLog2e);
+}
+
+template <int TPR, bool VEC>
+__global__ void __launch_bounds__(kCeThreads, 6)
+cross_entropy_rows_kernel(const float* logits, const int64_t* labels, float* row_loss, int batch, int classes,
+                          float inv_batch) {
+    constexpr int kTeams = kCeThreads / TPR;
+    const int lane = threadIdx.x % TPR;
+    const int team = threadIdx.x / TPR;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    pdl_wait();
+    float m = -INFINITY, s = 0.0f;
+    float picked = 0.0f;   // the logit of the row's label (lane 0), asked for before the row streams in
+    bool valid = false;
+    if (row < batch) {
+        const float* x = logits + row * classes;
+        if (lane == 0) {
+            const int64_t label = labels[row];
+            valid = label >= 0 && label < classes;
+            if (valid) picked = x[label];
+        }
+        const int items = VEC ? classes / 4 : classes;
+        for (int i0 = lane; i0 < items; i0 += TPR * kCeInFlight) {
+            float v[kCeInFlight][VEC ? 4 : 1];
+#pragma unroll
+            for (int u = 0; u < kCeInFlight; ++u) {
+                const int i = i0 + u * TPR;
+                if (VEC) {
+                    const float4 t = i < items ? ld_stream(reinterpret_cast<const float4*>(x) + i)
+                                               : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                    v[u][0] = t.x; v[u][1 % (VEC ? 4 : 1)] = t.y; v[u][2 % (VEC ? 4 : 1)] = t.z; v[u][3 % (VEC ? 4 : 1)] = t.w;
+                } else {
+                    v[u][0] = i < items ? ld_stream(x + i) : -INFINITY;
+                }
+            }
+            float m_new = m;
+#pragma unroll
+            for (int u = 0; u < kCeInFlight; ++u) {
+#pragma unroll
+                for (int k = 0; k < (VEC ? 4 : 1); ++k) m_new = fmaxf(m_new, v[u][k]);
+            }
+            // (x - max) first: the difference of equal values is exactly 0 whatever their size,
+            // which x * log2e - max * log2e does not guarantee for huge logits.
+            float add = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kCeInFlight; ++u) {
+#pragma unroll
+                for (int k = 0; k < (VEC ? 4 : 1); ++k) add += exp2_approx((v[u][k] - m_new) * kLog2e);
+            }
+            s = s * exp_diff(m, m_new) + add;
+            m = m_new;
+        }
     }
-    const float* x = logits + static_cast<int64_t>(row) * classes;
-    float m = -INFINITY;
-    for (int c = lane; c < classes; c += kWarp) m = fmaxf(m, x[c]);
-    m = warp_max(m);
-    float s = 0.0f;
-    for (int c = lane; c < classes; c += kWarp) s += expf(x[c] - m);
-    s = warp_sum(s);
-    if (lane == 0) row_loss[row] = (logf(s) + m - x[label]) * inv_batch;
+    pdl_trigger();
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) {
+        const float mo = __shfl_xor_sync(kFullMask, m, o);
+        const float so = __shfl_xor_sync(kFullMask, s, o);
+        const float m_new = fmaxf(m, mo);
+        s = s * exp_diff(m, m_new) + so * exp_diff(mo, m_new);
+        m = m_new;
+    }
+    if (lane == 0 && row < batch) row_loss[row] = valid ? (logf(s) + m - picked) * inv_batch : 0.0f;
+}
+
+template <int TPR>
+int launch_cross_entropy(bool vec, unsigned int grid, cudaStream_t stream, const float* logits, const int64_t* labels,
+                         float* row_loss, int batch, int classes, float inv_batch) {
+    const bool pdl = tuning().pdl != 0;
+    const dim3 g(grid), b(kCeThreads), one(1, 1, 1);
+    return vec ? launch_ex(cross_entropy_rows_kernel<TPR, true>, g, b, 0, stream, one, pdl, logits, labels, row_loss,
+                           batch, classes, inv_batch)
+               : launch_ex(cross_entropy_rows_kernel<TPR, false>, g, b, 0, stream, one, pdl, logits, labels, row_loss,
+                           batch, classes, inv_batch);
 }
 
 // ---- square transpose -------------------------------------------------------------------------------
+//
+// 64 x 64 tiles moved with 128-bit accesses in both directions.  A thread loads a 4 x 4
+// block (one float4 from each of four consecutive rows), transposes it in registers, and
+// parks the four resulting float4 in shared memory at the block's transposed position; after
+// the barrier every thread reads float4s in the order in which 16 consecutive lanes write
+// one 256-byte run of an output row.  The shared tile is [64][16] float4 without padding:
+// the float4 column is XOR-ed with (row / 4), which makes both the parking stores (lanes
+// differ in row / 4) and the reads (lanes differ in column) hit eight different 16-byte bank
+// groups per quarter warp.  (The reference's best form is a 32 x 33 padded tile with 4-byte
+// accesses, src/kernels/cuda/transpose.cu:54-69.)  Needs n % 4 == 0 and 16-byte aligned
+// pointers; other sizes take the scalar 32 x 33 kernel below.
+
+constexpr int kTr4Tile = 64;
+constexpr int kTr4Threads = 256;
+
+__global__ void __launch_bounds__(kTr4Threads)
+transpose_vec4_kernel(const float* in, float* out, int64_t n) {
+    __shared__ float4 tile[kTr4Tile][kTr4Tile / 4];
+    const int64_t npack = n / 4;
+    const int64_t bx = static_cast<int64_t>(blockIdx.x) * kTr4Tile;  // first input column of the tile
+    const int64_t by = static_cast<int64_t>(blockIdx.y) * kTr4Tile;  // first input row
+    const int c = threadIdx.x & 15;   // float4 column of the 4 x 4 block
+    const int i = threadIdx.x >> 4;   // block row
+    pdl_wait();
+    float4 v[4];
+    const int64_t cp = bx / 4 + c;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t r = by + 4 * i + k;
+        v[k] = (r < n && cp < npack) ? ld_stream(reinterpret_cast<const float4*>(in + r * n) + cp)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_trigger();
+    // Rows of the transposed block: output row 4c + j holds input rows 4i .. 4i+3 at column 4c + j.
+    tile[4 * c + 0][i ^ c] = make_float4(v[0].x, v[1].x, v[2].x, v[3].x);
+    tile[4 * c + 1][i ^ c] = make_float4(v[0].y, v[1].y, v[2].y, v[3].y);
+    tile[4 * c + 2][i ^ c] = make_float4(v[0].z, v[1].z, v[2].z, v[3].z);
+    tile[4 * c + 3][i ^ c] = make_float4(v[0].w, v[1].w, v[2].w, v[3].w);
+    __syncthreads();
+    const int p = threadIdx.x & 15;  // float4 column of the output row
+    const int64_t op = by / 4 + p;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int jr = (threadIdx.x >> 4) + 16 * k;  // output row within the tile
+        const int64_t r = bx + jr;
+        if (r < n && op < npack) st_stream(reinterpret_cast<float4*>(out + r * n) + op, tile[jr][p ^ (jr >> 2)]);
+    }
+}
 
 constexpr int kTrTile = 32;
 
@@ -72,62 +193,90 @@ transpose_kernel(const float* in, float* out, int64_t n) {
 // value range, so the generator is free: Philox is counter-based, needs no state and yields
 // four 32-bit words per call.
 
-__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
-    const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
-    c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+struct PhiloxKeys {
+    uint32_t k0[10];  // seed's low word + r * 0x9E3779B9: the key schedule, computed once on the host
+    uint32_t k1[10];  // seed's high word + r * 0xBB67AE85
+};
+
+PhiloxKeys philox_keys(uint64_t seed) {
+    PhiloxKeys k;
+    uint32_t a = static_cast<uint32_t>(seed), b = static_cast<uint32_t>(seed >> 32);
+    for (int r = 0; r < 10; ++r) {
+        k.k0[r] = a;
+        k.k1[r] = b;
+        a += 0x9E3779B9u;
+        b += 0xBB67AE85u;
+    }
+    return k;
 }
 
-__device__ __forceinline__ void philox4x32_10(uint64_t counter, uint64_t seed, uint32_t (&out)[4]) {
-    uint32_t c[4] = {static_cast<uint32_t>(counter), static_cast<uint32_t>(counter >> 32), 0u, 0u};
-    uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+// Ten rounds; each round is two 32 x 32 -> 64-bit products and two three-way XORs.
+__device__ __forceinline__ void philox4x32_10(uint64_t counter, const PhiloxKeys& keys, uint32_t (&out)[4]) {
+    uint32_t c0 = static_cast<uint32_t>(counter), c1 = static_cast<uint32_t>(counter >> 32), c2 = 0u, c3 = 0u;
 #pragma unroll
     for (int r = 0; r < 10; ++r) {
-        philox_round(c, k0, k1);
-        k0 += 0x9E3779B9u;
-        k1 += 0xBB67AE85u;
+        const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c0;
+        const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c2;
+        const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c1 ^ keys.k0[r];
+        const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c3 ^ keys.k1[r];
+        c1 = static_cast<uint32_t>(p1);
+        c3 = static_cast<uint32_t>(p0);
+        c0 = n0;
+        c2 = n2;
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) out[i] = c[i];
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
-// (0, 1]: never 0, so log() below is safe; same open/closed ends as curand_uniform.
+// (0, 1]: never 0, so the logarithm below is safe; same open/closed ends as curand_uniform.
 __device__ __forceinline__ float unit_open_closed(uint32_t w) {
-    return (static_cast<float>(w >> 8) + 1.0f) * (1.0f / 16777216.0f);
+    return fmaf(static_cast<float>(w >> 8), 1.0f / 16777216.0f, 1.0f / 16777216.0f);
 }
 
+// Two quads of floats per thread: 128-bit stores, and two independent Philox chains to
+// interleave.  NORMAL: Box-Muller on pairs with the hardware's approximate log2, square root
+// and sine / cosine (absolute error about 2^-21 each -- far below what a fill needs -- where the
+// exact routines cost several times the generator itself).
 template <bool NORMAL>
 __global__ void __launch_bounds__(256)
-random_fill_kernel(float* data, int64_t n, float p0, float p1, uint64_t seed) {
-    const int64_t quad = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-    const int64_t base = quad * 4;
-    if (base >= n) return;
-    uint32_t w[4];
-    philox4x32_10(static_cast<uint64_t>(quad), seed, w);
-    float v[4];
-    if (NORMAL) {
-        // Box-Muller on two pairs; p0 = mean, p1 = stddev.
+random_fill_kernel(float* data, int64_t n, float p0, float p1, const __grid_constant__ PhiloxKeys keys) {
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) * 2;  // first of the thread's two quads
+    float v[2][4];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const float u1 = unit_open_closed(w[2 * k]), u2 = unit_open_closed(w[2 * k + 1]);
-            const float r = sqrtf(-2.0f * logf(u1));
-            float sn, cs;
-            sincospif(2.0f * u2, &sn, &cs);
-            v[2 * k] = p0 + p1 * (r * cs);
-            v[2 * k + 1] = p0 + p1 * (r * sn);
+    for (int q = 0; q < 2; ++q) {
+        uint32_t w[4];
+        philox4x32_10(static_cast<uint64_t>(first + q), keys, w);
+        if (NORMAL) {
+            // p0 = mean, p1 = stddev.
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const float u1 = unit_open_closed(w[2 * k]), u2 = unit_open_closed(w[2 * k + 1]);
+                const float r = __fsqrt_rn(-1.3862943611198906f * __log2f(u1));  // sqrt(-2 ln u1)
+                float sn, cs;
+                __sincosf(6.283185307179586f * u2, &sn, &cs);
+                v[q][2 * k] = fmaf(p1, r * cs, p0);
+                v[q][2 * k + 1] = fmaf(p1, r * sn, p0);
+            }
+        } else {
+            // p0 = low, p1 = high.
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[q][k] = fmaf(unit_open_closed(w[k]), p1 - p0, p0);
         }
-    } else {
-        // p0 = low, p1 = high.
-#pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = p0 + unit_open_closed(w[k]) * (p1 - p0);
     }
-    if (base + 3 < n && aligned16_dev(data)) {
-        reinterpret_cast<float4*>(data)[quad] = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
+    // The values depend on nothing in memory: only the stores have to wait for the previous
+    // kernel of the stream (which may still be reading this buffer).
+    pdl_wait();
+    pdl_trigger();
+    const bool vec = aligned16_dev(data);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (base + k < n) data[base + k] = v[k];
+    for (int q = 0; q < 2; ++q) {
+        const int64_t base = (first + q) * 4;
+        if (base + 3 < n && vec) {
+            st_stream(reinterpret_cast<float4*>(data) + first + q, make_float4(v[q][0], v[q][1], v[q][2], v[q][3]));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (base + k < n) data[base + k] = v[q][k];
+            }
         }
     }
 }
@@ -147,17 +296,28 @@ int fdl_cross_entropy_f32(const float* logits, const int64_t* labels, float* los
     cudaStream_t s = as_stream(stream);
     if (batch == 0) return static_cast<int>(cudaMemsetAsync(loss, 0, sizeof(float), s));
     if (logits == nullptr || labels == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    const bool vec = classes % 4 == 0 && aligned16(logits);
+    // A team of lanes per row: about eight items (packs on the 128-bit path) per lane.
+    const int64_t items = vec ? classes / 4 : classes;
+    int tpr = 1;
+    while (tpr < kWarp && static_cast<int64_t>(tpr) * kCeInFlight < items) tpr <<= 1;
+    const int64_t grid = ceil_div(batch, kCeThreads / tpr);
     const size_t sum_bytes = fdl_sum_scratch_bytes(batch);
     void* ws = nullptr;
     int status = get_workspace(sum_bytes + static_cast<size_t>(batch) * sizeof(float) + 256, &ws);
     if (status != FDL_OK) return status;
     float* row_loss = reinterpret_cast<float*>(static_cast<char*>(ws) + sum_bytes);
-    const int rows_per_cta = kCeThreads / kWarp;
-    const unsigned int grid = static_cast<unsigned int>(ceil_div(batch, rows_per_cta));
-    cross_entropy_rows_kernel<<<grid, kCeThreads, 0, s>>>(
-        logits, labels, row_loss, static_cast<int>(batch), static_cast<int>(classes),
-        1.0f / static_cast<float>(batch));
-    status = launch_status();
+    const unsigned int g = static_cast<unsigned int>(grid);
+    const int b = static_cast<int>(batch), c = static_cast<int>(classes);
+    const float inv_batch = 1.0f / static_cast<float>(batch);
+    switch (tpr) {
+        case 1: status = launch_cross_entropy<1>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        case 2: status = launch_cross_entropy<2>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        case 4: status = launch_cross_entropy<4>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        case 8: status = launch_cross_entropy<8>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        case 16: status = launch_cross_entropy<16>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        default: status = launch_cross_entropy<32>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+    }
     if (status != FDL_OK) return status;
     return fdl_sum_f32(row_loss, batch, loss, nullptr, ws, sum_bytes, stream);
 }
@@ -166,6 +326,13 @@ int fdl_transpose_f32(const float* in, float* out, int64_t n, void* stream) {
     if (n < 0) return FDL_ERR_INVALID_ARGUMENT;
     if (n == 0) return FDL_OK;
     if (in == nullptr || out == nullptr || in == out) return FDL_ERR_INVALID_ARGUMENT;
+    if (n % 4 == 0 && aligned16(in) && aligned16(out)) {
+        const int64_t tiles = ceil_div(n, kTr4Tile);
+        if (tiles > 65535) return FDL_ERR_UNSUPPORTED;
+        const dim3 grid(static_cast<unsigned int>(tiles), static_cast<unsigned int>(tiles));
+        return launch_ex(transpose_vec4_kernel, grid, dim3(kTr4Threads), 0, as_stream(stream), dim3(1, 1, 1),
+                         tuning().pdl != 0, in, out, n);
+    }
     const int64_t tiles = ceil_div(n, kTrTile);
     if (tiles > 65535) return FDL_ERR_UNSUPPORTED;
     const dim3 grid(static_cast<unsigned int>(tiles), static_cast<unsigned int>(tiles));
@@ -173,24 +340,24 @@ int fdl_transpose_f32(const float* in, float* out, int64_t n, void* stream) {
     return launch_status();
 }
 
-int fdl_uniform_f32(float* data, int64_t n, float low, float high, uint64_t seed, void* stream) {
+static int random_fill(bool normal, float* data, int64_t n, float p0, float p1, uint64_t seed, void* stream) {
     if (n < 0 || (n > 0 && data == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
     if (n == 0) return FDL_OK;
-    const int64_t grid = ceil_div(ceil_div(n, 4), 256);
+    const int64_t grid = ceil_div(ceil_div(n, 8), 256);  // eight floats per thread
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
-    random_fill_kernel<false><<<static_cast<unsigned int>(grid), 256, 0, as_stream(stream)>>>(
-        data, n, low, high, seed);
-    return launch_status();
+    const dim3 g(static_cast<unsigned int>(grid)), b(256), one(1, 1, 1);
+    const PhiloxKeys keys = philox_keys(seed);
+    const bool pdl = tuning().pdl != 0;
+    return normal ? launch_ex(random_fill_kernel<true>, g, b, 0, as_stream(stream), one, pdl, data, n, p0, p1, keys)
+                  : launch_ex(random_fill_kernel<false>, g, b, 0, as_stream(stream), one, pdl, data, n, p0, p1, keys);
+}
+
+int fdl_uniform_f32(float* data, int64_t n, float low, float high, uint64_t seed, void* stream) {
+    return random_fill(false, data, n, low, high, seed, stream);
 }
 
 int fdl_normal_f32(float* data, int64_t n, float mean, float stddev, uint64_t seed, void* stream) {
-    if (n < 0 || (n > 0 && data == nullptr)) return FDL_ERR_INVALID_ARGUMENT;
-    if (n == 0) return FDL_OK;
-    const int64_t grid = ceil_div(ceil_div(n, 4), 256);
-    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
-    random_fill_kernel<true><<<static_cast<unsigned int>(grid), 256, 0, as_stream(stream)>>>(
-        data, n, mean, stddev, seed);
-    return launch_status();
+    return random_fill(true, data, n, mean, stddev, seed, stream);
 }
 
 }  // extern "C"

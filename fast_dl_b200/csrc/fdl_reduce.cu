@@ -204,15 +204,16 @@ __device__ __forceinline__ double block_sum_double(double v, double* red) {
 // separate collective kernel.  Two parities make it safe to start epoch e+1 while a slow
 // peer still reads e.
 constexpr int kMaxRanks = 16;
-constexpr unsigned long long kExchangeWaitNs = 2000000000ull;  // 2 s, then give up
 
 struct SumExchange {
     int world = 0;  // 0: single GPU, no exchange
     int rank = 0;
     int send_only = 0;  // 1: split-phase start -- send the partial, leave waiting to the finish kernel
     unsigned int epoch = 0;
+    unsigned long long wait_ns = 2000000000ull;  // how long to wait for the peers before giving up
     unsigned long long* words[kMaxRanks] = {};  // each rank's buffer
     unsigned int* error_flag = nullptr;
+    unsigned long long* trace = nullptr;  // not NULL: eight time stamps of the finishing CTA go here
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -229,6 +230,7 @@ struct ColsExchange {
     int world = 0;  // 0: single GPU, no exchange
     int rank = 0;
     unsigned int epoch = 0;
+    unsigned long long wait_ns = 2000000000ull;
     unsigned long long* words[kMaxRanks] = {};  // each rank's vector region
     unsigned int* error_flag = nullptr;
 };
@@ -251,7 +253,7 @@ __device__ __forceinline__ float exchange_column(const ColsExchange& xc, int64_t
         unsigned long long w = *src;
         unsigned int polls = 0;
         while ((w & 0xffffffffull) != tag) {
-            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
+            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > xc.wait_ns) {
                 atomicOr(xc.error_flag, 2u);
                 return nanf("");
             }
@@ -288,7 +290,7 @@ __device__ __forceinline__ double exchange_fold_partials(const SumExchange& xc) 
         unsigned long long w0 = src[0], w1 = src[1];
         unsigned int polls = 0;
         while ((w0 & 0xffffffffull) != tag || (w1 & 0xffffffffull) != tag) {
-            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > kExchangeWaitNs) {
+            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > xc.wait_ns) {
                 ok = false;
                 break;
             }
@@ -333,6 +335,8 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
     // Arrive now, wait just before the first remote shared-memory access: by then every
     // CTA of the cluster is known to be running, which DSMEM stores require.
     if (CL > 1) cluster.barrier_arrive();
+    if (xc.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) xc.trace[0] = global_timer_ns();
+    pdl_wait();  // the input may be the previous kernel's output; the scratch was its scratch
 
     float acc = 0.0f;
     if (VEC) {
@@ -374,6 +378,7 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
         }
     }
 
+    pdl_trigger();  // every load of this CTA has been issued
     const double block_total = block_sum_double<kSumThreads>(static_cast<double>(acc), red);
 
     unsigned int nclusters = gridDim.x;
@@ -408,57 +413,59 @@ sum_kernel(const float* x, int64_t n, int64_t nvec, float* out_f32, double* out_
     if (!is_last) return;
 
     // The last cluster leader folds all partials in index order.
+    const bool tracing = xc.trace != nullptr && threadIdx.x == 0;
+    long long c_ticket = 0;
+    if (tracing) {
+        xc.trace[1] = global_timer_ns();
+        c_ticket = clock64();
+    }
     __threadfence();
     double t = 0.0;
     for (unsigned int k = threadIdx.x; k < nclusters; k += kSumThreads) t += __ldcg(partials + k);
     double total = block_sum_double<kSumThreads>(t, red);
+    if (tracing) xc.trace[2] = global_timer_ns();
     if (xc.world > 0) {
         __shared__ double my_total;
         if (threadIdx.x == 0) my_total = total;
         __syncthreads();
         if (threadIdx.x < xc.world) exchange_send_partial(xc, threadIdx.x, my_total);
+        if (tracing) xc.trace[3] = global_timer_ns();
         if (xc.send_only) {
             if (threadIdx.x == 0) *counter = 0;
             return;
         }
         total = exchange_fold_partials(xc);
+        if (tracing) xc.trace[4] = global_timer_ns();
     }
     if (threadIdx.x == 0) {
         if (out_f32 != nullptr) *out_f32 = static_cast<float>(total);
         if (out_f64 != nullptr) *out_f64 = total;
         *counter = 0;  // ready for the next launch
     }
+    if (tracing) {
+        xc.trace[5] = global_timer_ns();
+        xc.trace[6] = static_cast<unsigned long long>(clock64() - c_ticket);  // SM cycles, ticket to end
+        xc.trace[7] = xc.epoch;
+    }
 }
 
 template <int CL, bool VEC>
 int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsigned int* counter,
-               double* partials, cudaStream_t stream, const SumExchange& xc = SumExchange()) {
+               double* partials, cudaStream_t stream, SumExchange xc = SumExchange(), bool pdl = true) {
     const int64_t nvec = VEC ? n / 4 : 0;
     int64_t tiles = VEC ? ceil_div(nvec, kSumTile) : ceil_div(n, static_cast<int64_t>(kSumTile) * 4);
     if (tiles < 1) tiles = 1;
     int64_t grid = ceil_div(tiles, CL) * CL;
     const int64_t cap = static_cast<int64_t>(kSumMaxPartials) * CL;
     if (grid > cap) grid = cap;
-    if (CL == 1) {
-        sum_kernel<1, VEC><<<static_cast<unsigned int>(grid), kSumThreads, 0, stream>>>(
-            x, n, nvec, out_f32, out_f64, counter, partials, xc);
-        return launch_status();
+    if (tuning().sum_trace != 0) {
+        unsigned int* flag = nullptr;
+        const int st = error_flag_device_ptr(&flag);
+        if (st != FDL_OK) return st;
+        xc.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(flag) + 64);
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned int>(grid));
-    cfg.blockDim = dim3(kSumThreads);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = CL;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, sum_kernel<CL, VEC>, x, n, nvec, out_f32, out_f64,
-                                       counter, partials, xc);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    return launch_status();
+    return launch_ex(sum_kernel<CL, VEC>, dim3(static_cast<unsigned int>(grid)), dim3(kSumThreads), 0, stream,
+                     dim3(CL, 1, 1), pdl && tuning().pdl != 0, x, n, nvec, out_f32, out_f64, counter, partials, xc);
 }
 
 // ======================================================================================
@@ -1451,8 +1458,9 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
     unsigned int* counter = static_cast<unsigned int*>(scratch);
     double* partials = reinterpret_cast<double*>(static_cast<char*>(scratch) + kStaticCounterBytes);
     // Fixed launch shape (clusters of 4): at most kSumMaxPartials partials are written.
-    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s);
-    return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s);
+    // Plain launches: the memset above, not a kernel, is what precedes them on the stream.
+    if (!aligned16(x)) return launch_sum<1, false>(x, n, out_f32, out_f64, counter, partials, s, SumExchange(), false);
+    return launch_sum<4, true>(x, n, out_f32, out_f64, counter, partials, s, SumExchange(), false);
 }
 
 int fdl_reduce_rows_f32(const float* x, int64_t rows, int64_t cols, float* out, int op,
@@ -1552,6 +1560,14 @@ static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t
         else { if (vec) FDL_LAUNCH_COLS(ColSum, 4, CL); else FDL_LAUNCH_COLS(ColSum, 1, CL); }  \
     } while (0)
     switch (g.cluster) {
+        case 16: {  // beyond the portable cluster size: every instantiation has to opt in
+            cudaFuncSetAttribute(reduce_cols_kernel<ColMax, 4, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(reduce_cols_kernel<ColMax, 1, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(reduce_cols_kernel<ColSum, 4, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(reduce_cols_kernel<ColSum, 1, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            FDL_LAUNCH_COLS_CL(16);
+            break;
+        }
         case 8: FDL_LAUNCH_COLS_CL(8); break;
         case 4: FDL_LAUNCH_COLS_CL(4); break;
         case 2: FDL_LAUNCH_COLS_CL(2); break;
@@ -1595,6 +1611,7 @@ struct ExchangeContext {
     void* local = nullptr;
     void* peer[kMaxRanks] = {};
     bool connected = false;
+    bool by_pointer = false;  // peers were given as device pointers (same process): nothing to close
 };
 
 }  // namespace
@@ -1647,11 +1664,30 @@ int fdl_exchange_connect(void* ctx_in, const unsigned char* handles) {
     return FDL_OK;
 }
 
+int fdl_exchange_buffer(void* ctx_in, void** buffer_out) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || buffer_out == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    *buffer_out = ctx->local;
+    return FDL_OK;
+}
+
+int fdl_exchange_connect_pointers(void* ctx_in, void* const* buffers) {
+    auto* ctx = static_cast<ExchangeContext*>(ctx_in);
+    if (ctx == nullptr || buffers == nullptr || ctx->connected) return FDL_ERR_INVALID_ARGUMENT;
+    for (int p = 0; p < ctx->world; ++p) {
+        if (buffers[p] == nullptr || (p == ctx->rank && buffers[p] != ctx->local)) return FDL_ERR_INVALID_ARGUMENT;
+    }
+    for (int p = 0; p < ctx->world; ++p) ctx->peer[p] = buffers[p];
+    ctx->by_pointer = true;
+    ctx->connected = true;
+    return FDL_OK;
+}
+
 int fdl_exchange_destroy(void* ctx_in) {
     auto* ctx = static_cast<ExchangeContext*>(ctx_in);
     if (ctx == nullptr) return FDL_OK;
     cudaDeviceSynchronize();
-    for (int p = 0; p < ctx->world; ++p) {
+    for (int p = 0; p < ctx->world && !ctx->by_pointer; ++p) {
         if (p != ctx->rank && ctx->peer[p] != nullptr) cudaIpcCloseMemHandle(ctx->peer[p]);
     }
     cudaFree(ctx->local);
@@ -1663,6 +1699,7 @@ static int sum_exchange_fill(ExchangeContext* ctx, SumExchange* xc) {
     xc->world = ctx->world;
     xc->rank = ctx->rank;
     xc->epoch = ctx->epoch;
+    xc->wait_ns = static_cast<unsigned long long>(tuning().exchange_wait_ms) * 1000000ull;
     for (int p = 0; p < ctx->world; ++p) xc->words[p] = static_cast<unsigned long long*>(ctx->peer[p]);
     return error_flag_device_ptr(&xc->error_flag);
 }
@@ -1735,6 +1772,7 @@ int fdl_reduce_cols_allreduce_f32(const float* x, int64_t rows, int64_t cols, fl
     ctx->epoch_cols += 1;
     if (ctx->epoch_cols == 0) ctx->epoch_cols = 1;
     xc.epoch = ctx->epoch_cols;
+    xc.wait_ns = static_cast<unsigned long long>(tuning().exchange_wait_ms) * 1000000ull;
     for (int p = 0; p < ctx->world; ++p) {
         xc.words[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx->peer[p]) + kExchangeSumBytes);
     }

@@ -1,5 +1,6 @@
 // Runtime plumbing of the C ABI: device selection, error text, cached device
 // properties and the library-owned per-device workspace.
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -34,8 +35,8 @@ int error_flag_device_ptr(unsigned int** dev) {
             void* h = nullptr;
             cudaError_t e = cudaHostAlloc(&h, 256, cudaHostAllocMapped | cudaHostAllocPortable);
             if (e != cudaSuccess) return static_cast<int>(e);
+            memset(h, 0, 256);
             g_error_flag_host = static_cast<unsigned int*>(h);
-            *g_error_flag_host = 0;
         }
     }
     void* d = nullptr;
@@ -43,6 +44,12 @@ int error_flag_device_ptr(unsigned int** dev) {
     if (e != cudaSuccess) return static_cast<int>(e);
     *dev = static_cast<unsigned int*>(d);
     return FDL_OK;
+}
+
+const unsigned long long* trace_words_host() {
+    return g_error_flag_host == nullptr
+               ? nullptr
+               : reinterpret_cast<const unsigned long long*>(reinterpret_cast<const char*>(g_error_flag_host) + 64);
 }
 
 unsigned int read_and_clear_device_error_flag() {
@@ -160,7 +167,7 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().cols_tx = value;
         return FDL_OK;
     }
-    if (k == "cols_cluster" && (value == 1 || value == 2 || value == 4 || value == 8)) {
+    if (k == "cols_cluster" && (value == 1 || value == 2 || value == 4 || value == 8 || value == 16)) {
         fdl::tuning().cols_cluster = value;
         return FDL_OK;
     }
@@ -184,7 +191,36 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().rows_staged = value;
         return FDL_OK;
     }
+    if (k == "pdl" && (value == 0 || value == 1)) {
+        fdl::tuning().pdl = value;
+        return FDL_OK;
+    }
+    if (k == "exchange_wait_ms" && value >= 1 && value <= 60000) {
+        fdl::tuning().exchange_wait_ms = value;
+        return FDL_OK;
+    }
+    if (k == "sum_trace" && (value == 0 || value == 1)) {
+        fdl::tuning().sum_trace = value;
+        return FDL_OK;
+    }
+    if (k == "bcast2d_rows" && (value == 0 || value == 1 || value == 2 || value == 4)) {
+        fdl::tuning().bcast2d_rows = value;
+        return FDL_OK;
+    }
+    if (k == "bcast2d" && (value == 0 || value == 1)) {
+        fdl::tuning().bcast2d = value;
+        return FDL_OK;
+    }
     return FDL_ERR_INVALID_ARGUMENT;
+}
+
+int fdl_debug_sum_trace(unsigned long long* out8) {
+    if (out8 == nullptr) return FDL_ERR_INVALID_ARGUMENT;
+    const unsigned long long* w = fdl::trace_words_host();
+    for (int i = 0; i < fdl::kTraceWords; ++i) {
+        out8[i] = w == nullptr ? 0ull : reinterpret_cast<const volatile unsigned long long*>(w)[i];
+    }
+    return FDL_OK;
 }
 
 int fdl_device_count(void) {

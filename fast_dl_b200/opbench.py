@@ -157,6 +157,31 @@ def main(ref=None) -> None:
             record("c4", f"activation {name}", 8 * R * C, lambda op=op: capi.unary(L, op, out=out),
                    (lambda op=op: ref.gpu_activation(L.data_ptr(), out.data_ptr(), R * C, op)) if ref else None)
 
+    if "next" in cfgs:  # the path's neighbours: cross-entropy, square transpose, random fill
+        R, C = 65536, 1024
+        L = normal((R, C), 3.0)
+        labels = torch.randint(0, C, (R,), device=dev, generator=gen)
+        loss = torch.empty(1, dtype=torch.float32, device=dev)
+        record("nxt", "cross-entropy [65536,1024]", 4 * R * C + 8 * R + 4, lambda: capi.cross_entropy(L, labels),
+               (lambda: ref.gpu_cross_entropy(L.data_ptr(), labels.data_ptr(), loss.data_ptr(), R, C)) if ref else None)
+        del L
+        for n in (4096, 8192, 16384):
+            X = normal((n, n))
+            out = torch.empty_like(X)
+            record("nxt", f"transpose [{n},{n}]", 8 * n * n,
+                   lambda: capi.check(capi.lib().fdl_transpose_f32(X.data_ptr(), out.data_ptr(), n, capi._stream()), "transpose"),
+                   (lambda: ref.gpu_transpose(X.data_ptr(), out.data_ptr(), n, 2)) if ref else None)
+            del X, out
+        n = 1 << 28
+        buf = torch.empty(n, dtype=torch.float32, device=dev)
+        record("nxt", "uniform fill, 2^28 floats", 4 * n,
+               lambda: capi.check(capi.lib().fdl_uniform_f32(buf.data_ptr(), n, -1.0, 1.0, 1234, capi._stream()), "uniform"),
+               (lambda: ref.gpu_uniform(buf.data_ptr(), n, -1.0, 1.0, 1234)) if ref else None)
+        record("nxt", "normal fill, 2^28 floats", 4 * n,
+               lambda: capi.check(capi.lib().fdl_normal_f32(buf.data_ptr(), n, 0.0, 1.0, 1234, capi._stream()), "normal"),
+               (lambda: ref.gpu_normal(buf.data_ptr(), n, 0.0, 1.0, 1234)) if ref else None)
+        del buf
+
     if "rows" in cfgs:  # extra row-wise shapes: short and long rows
         for R, C in ((1 << 21, 32), (1 << 20, 64), (1 << 19, 128), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384),
                      (2048, 32768), (1024, 65536), (512, 131072), (128, 524288)):

@@ -39,6 +39,11 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden visibility; only the entry points declared here are exported. */
+#if defined(FDL_BUILDING_LIBRARY) && defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 #define FDL_OK 0
 #define FDL_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, bad enum          */
 #define FDL_ERR_UNSUPPORTED (-2)      /* shape outside what the entry point implements   */
@@ -105,10 +110,26 @@ int fdl_take_device_error(void);
  * -1 = whichever measured faster for the op and length; default -1), "rows_cluster_threads"
  * (256 or 512 threads per CTA in the cluster form of rows of 16388..65536 floats; default 256),
  * and for the column reductions "cols_tx" (threads across columns per CTA: 16..256; default
- * 64), "cols_cluster" (1, 2, 4, 8; default 4), "cols_ctas_per_sm" (default 4) and
- * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default).
+ * 64), "cols_cluster" (1, 2, 4, 8, 16; default 4), "cols_ctas_per_sm" (default 4) and
+ * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default);
+ * "pdl" (1 = the streaming kernels are launched with programmatic stream serialization, so
+ * that the next kernel's launch overlaps the tail of the one before; 0 = plain launches;
+ * default 1), "bcast2d" (1 = two-dimensional broadcasts take the division-free kernel;
+ * default 1) and "bcast2d_rows" (rows per thread there: 1, 2, 4, or 0 = by size).
+ * Two keys are not launch shapes: "exchange_wait_ms" (1..60000, default 2000) is how long a
+ * cross-GPU exchange waits for its peers before it gives up, and "sum_trace" (0 / 1) makes the
+ * full sum's finishing CTA record time stamps for fdl_debug_sum_trace.
  * Not part of the reference's interface. */
 int fdl_set_tuning(const char* key, int value);
+
+/* Measurement aid: with the tuning key "sum_trace" set, the CTA that finishes a full sum
+ * (fdl_sum_f32, fdl_sum_allreduce_f32) leaves eight 64-bit words in host-visible memory; this
+ * copies the words of the most recent such kernel.  Words 0-5 are %globaltimer values in
+ * nanoseconds: [0] first CTA started, [1] last cluster arrived (ticket taken), [2] partials
+ * folded, [3] partial sent to the peers, [4] all peers' partials seen, [5] result written
+ * ([3], [4] only with an exchange); [6] SM cycles from [1] to [5]; [7] the exchange epoch.
+ * Read after the stream has been synchronised.  Not part of the reference's interface. */
+int fdl_debug_sum_trace(unsigned long long* out8);
 
 /* ---- elementwise ------------------------------------------------------------------ */
 
@@ -191,14 +212,16 @@ int fdl_sum_f32(const float* x, int64_t n, float* out_f32, double* out_f64,
 /* Full sum for callers that cannot allocate device memory: a host framework whose own
  * allocator must account for every device byte, a service whose device-memory budget is
  * fixed at start-up, or latency-critical code that must not enter the driver's allocator
- * (cudaMalloc and cudaFree synchronise the device).  Same result as fdl_sum_f32, but the scratch is a fixed 65,792-byte
+ * (cudaMalloc and cudaFree synchronise the device).  Same result as fdl_sum_f32 at its default
+ * launch shape (clusters of 4; the tuning key "sum_cluster" does not apply here), but the scratch is a fixed 65,792-byte
  * array in the library's device image instead of caller- or library-allocated memory, and
  * the call performs no cudaMalloc/cudaFree or any other allocating routine.
  *   - n may be at most 2^30 (1,073,741,824) elements; larger n returns
  *     FDL_ERR_TOO_LARGE_FOR_STATIC_SCRATCH without launching anything.
  *   - The first call on each device looks the array's device address up (one
  *     cudaGetSymbolAddress with that device current); make that first call before any
- *     stream capture begins.
+ *     stream capture begins.  The address is kept for the life of the device's primary
+ *     context: after a cudaDeviceReset the library must be reloaded.
  *   - All calls on a device share the one array: the arrival counter in it is cleared on
  *     the stream at the start of every call, and two calls whose kernels may overlap on
  *     the GPU (different streams without an ordering between them) race on it.  Serialise
@@ -212,7 +235,7 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
  * fdl_sum_allreduce_f32 is fdl_sum_f32 plus the exchange of the per-GPU partials, in ONE
  * kernel: the CTA that finishes a rank's sum stores the partial into a small buffer of every
  * peer over NVLink (plain 8-byte peer stores that carry an epoch tag, no multicast), waits --
- * at most two seconds -- for the peers' tagged values in its own buffer and adds them in rank order,
+ * at most two seconds (tuning key "exchange_wait_ms") -- for the peers' tagged values in its own buffer and adds them in rank order,
  * so every rank ends with the same bits and no separate collective kernel is launched.
  * A wait that runs out writes NaN to the outputs and raises the flag read by
  * fdl_take_device_error; it never hangs.
@@ -226,6 +249,12 @@ int fdl_sum_f32_static(const float* x, int64_t n, float* out_f32, double* out_f6
 int fdl_exchange_create(int world, int rank, void** ctx_out);
 int fdl_exchange_local_handle(void* ctx, unsigned char* handle64);
 int fdl_exchange_connect(void* ctx, const unsigned char* handles);
+/* For ranks that live in ONE process (one host thread driving several GPUs with peer access
+ * enabled, or several contexts on one GPU): fdl_exchange_buffer returns the device pointer of
+ * a context's own buffer, and fdl_exchange_connect_pointers takes all ranks' buffers, in rank
+ * order, in place of the IPC handles.  No counterpart in the reference. */
+int fdl_exchange_buffer(void* ctx, void** buffer_out);
+int fdl_exchange_connect_pointers(void* ctx, void* const* buffers);
 int fdl_exchange_destroy(void* ctx);
 int fdl_sum_allreduce_f32(const float* x, int64_t n, float* out_f32, double* out_f64, void* ctx,
                           void* scratch, size_t scratch_bytes, void* stream);
@@ -350,6 +379,10 @@ int fdl_host_sum_f32(const float* h_x, int64_t n, double* h_out);
  * 2 down instead of 4 up and 2 down for three separate calls. */
 int fdl_host_sweep_f32(const float* h_x, const float* h_y, const float* h_row, float* h_z,
                        float* h_w, int64_t rows, int64_t cols, double* h_sum);
+
+#if defined(FDL_BUILDING_LIBRARY) && defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 } /* extern "C" */

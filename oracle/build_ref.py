@@ -12,7 +12,8 @@ previously built files (if any) are used as they are.
 
 Outputs
   oracle/_ref/libref.so       - the reference's CUDA kernels for the path (elementwise,
-                                activation, vector_add, bias, reduction, softmax, layernorm),
+                                activation, vector_add, bias, reduction, softmax, layernorm) and
+                                its neighbours (cross_entropy, transpose, random),
                                 recompiled for sm_100a, plus the CPU check functions that live
                                 in its tests/benchmarks, all behind the C shims of
                                 oracle/ref_shims/*.cpp.  CPU flags: g++ -O2 -ffp-contract=off
@@ -48,7 +49,8 @@ REF = Path(os.environ.get("REFERENCE_ROOT", str(ROOT.parent / "reference")))
 OUT = HERE / "_ref"
 SHIMS = HERE / "ref_shims"
 
-REF_KERNELS = ["elementwise", "activation", "vector_add", "bias", "reduction", "softmax", "layernorm"]
+REF_KERNELS = ["elementwise", "activation", "vector_add", "bias", "reduction", "softmax", "layernorm",
+               "cross_entropy", "transpose", "random"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CPU_FLAGS = ["-O2", "-ffp-contract=off", "-std=c++17", "-fPIC"]
 

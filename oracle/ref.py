@@ -131,3 +131,22 @@ def gpu_softmax(x, y, rows, cols, algo=2):
 def gpu_layernorm(x, y, rows, cols, eps=1e-5):
     _chk(lib().ref_gpu_layernorm(C.c_void_p(x), C.c_void_p(y), C.c_int(rows), C.c_int(cols), C.c_float(eps)),
          "layernorm")
+
+
+def gpu_cross_entropy(logits, labels, loss, batch, classes):
+    _chk(lib().ref_gpu_cross_entropy(C.c_void_p(logits), C.c_void_p(labels), C.c_void_p(loss), C.c_int(batch),
+                                     C.c_int(classes)), "cross_entropy")
+
+
+def gpu_transpose(x, y, n, algo=2):
+    _chk(lib().ref_gpu_transpose(C.c_void_p(x), C.c_void_p(y), _sz(n), C.c_int(algo)), "transpose")
+
+
+def gpu_uniform(data, n, low, high, seed):
+    _chk(lib().ref_gpu_uniform(C.c_void_p(data), C.c_longlong(n), C.c_float(low), C.c_float(high),
+                               C.c_ulonglong(seed)), "uniform")
+
+
+def gpu_normal(data, n, mean, stddev, seed):
+    _chk(lib().ref_gpu_normal(C.c_void_p(data), C.c_longlong(n), C.c_float(mean), C.c_float(stddev),
+                              C.c_ulonglong(seed)), "normal")

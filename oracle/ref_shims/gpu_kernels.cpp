@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <cstdint>
 
 #include <dl/kernels/kernels.hpp>
 
@@ -40,6 +41,25 @@ int ref_gpu_softmax(const float* x, float* y, std::size_t rows, std::size_t cols
 }
 int ref_gpu_layernorm(const float* x, float* y, int rows, int cols, float eps) {
     k::layernorm(x, y, rows, cols, eps);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int ref_gpu_cross_entropy(const float* logits, const long long* labels, float* loss, int batch, int classes) {
+    // as dl::ops::cross_entropy does (src/ops/CrossEntropy.cpp): the kernel accumulates into *loss
+    cudaMemset(loss, 0, sizeof(float));
+    k::cross_entropy(logits, reinterpret_cast<const int64_t*>(labels), loss, batch, classes);
+    return static_cast<int>(cudaGetLastError());
+}
+int ref_gpu_transpose(const float* in, float* out, std::size_t n, int algo) {
+    k::transpose(in, out, n, static_cast<k::TransposeAlgo>(algo));
+    return static_cast<int>(cudaGetLastError());
+}
+int ref_gpu_uniform(float* data, long long n, float low, float high, unsigned long long seed) {
+    k::uniform_float32(data, n, low, high, seed);
+    return static_cast<int>(cudaGetLastError());
+}
+int ref_gpu_normal(float* data, long long n, float mean, float stddev, unsigned long long seed) {
+    k::normal_float32(data, n, mean, stddev, seed);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -56,7 +56,8 @@ def test_every_documented_tuning_key_is_accepted(fdl):
     doc = header[header.index("Measurement aid: selects a launch shape"):header.index("int fdl_set_tuning")]
     keys = re.findall(r'"([a-z0-9_]+)"', doc)
     defaults = {"sum_cluster": 4, "rows_staged": -1, "rows_warp16": -1, "rows_cluster_threads": 256,
-                "cols_tx": 64, "cols_cluster": 4, "cols_ctas_per_sm": 4, "cols_chunks": 0}
+                "cols_tx": 64, "cols_cluster": 4, "cols_ctas_per_sm": 4, "cols_chunks": 0,
+                "pdl": 1, "bcast2d": 1, "bcast2d_rows": 0, "exchange_wait_ms": 2000, "sum_trace": 0}
     assert sorted(keys) == sorted(defaults), keys
     lib = fdl.lib()
     for key, value in defaults.items():
@@ -64,6 +65,22 @@ def test_every_documented_tuning_key_is_accepted(fdl):
     assert lib.fdl_set_tuning(b"no_such_key", 1) != 0
     assert lib.fdl_set_tuning(b"sum_cluster", 3) != 0
     assert lib.fdl_set_tuning(b"rows_cluster_threads", 128) != 0
+    assert lib.fdl_set_tuning(b"exchange_wait_ms", 0) != 0
+
+
+def test_library_exports_nothing_but_the_c_abi(fdl):
+    """The dynamic symbol table of the library holds the fdl_* entry points and no C++ symbol
+    of its internals (it is built with hidden visibility)."""
+    import shutil
+    import subprocess
+    if shutil.which("nm") is None:
+        pytest.skip("no nm")
+    out = subprocess.run(["nm", "-D", "--defined-only", str(fdl.library_path())], check=True, capture_output=True,
+                         text=True).stdout
+    names = [line.split()[-1] for line in out.splitlines() if line.strip()]
+    foreign = [n for n in names if not n.startswith("fdl_")]
+    assert not foreign, f"exported besides the C ABI: {foreign[:10]}"
+    assert sorted(n for n in names if n.startswith("fdl_")) == declared_symbols()
 
 
 def test_header_is_plain_c(tmp_path):

@@ -163,6 +163,53 @@ def test_broadcast_bit_exact(fdl, cuda, sa, sb):
         assert_bit_exact(got, orc.broadcast_binary(a, b, op), f"{sa} {sb} op{op}")
 
 
+@pytest.mark.parametrize("rows,cols", [(1, 4), (5, 8), (1000, 64), (777, 1028), (4096, 4096), (3, 40000), (70000, 16)])
+@pytest.mark.parametrize("rows_per_thread", [0, 1, 2, 4])
+def test_two_dimensional_broadcast_forms(fdl, cuda, rows, cols, rows_per_thread):
+    """Every pairing of operand kinds of the two-dimensional kernel -- dense rows, a [1, C] row vector, an
+    [R, 1] column vector -- for every rows-per-thread variant, plus a dense operand that is a column
+    window of a wider matrix (row stride larger than the row) and the in-place use."""
+    import ctypes as C
+    rng = np.random.default_rng(46)
+    dense = rng.normal(size=(rows, cols)).astype(np.float32)
+    rowv = rng.uniform(0.5, 2.0, size=(1, cols)).astype(np.float32)
+    colv = rng.uniform(0.5, 2.0, size=(rows, 1)).astype(np.float32)
+    fdl.set_tuning("bcast2d_rows", rows_per_thread)
+    try:
+        for a, b in ((dense, rowv), (rowv, dense), (dense, colv), (colv, dense), (colv, rowv), (rowv, colv)):
+            for op in (fdl.ADD, fdl.DIV):
+                got = to_np(fdl.broadcast_binary(dev(cuda, a), dev(cuda, b), op))
+                assert_bit_exact(got, orc.broadcast_binary(a, b, op), f"{a.shape} {b.shape} op{op}")
+        # a window [rows, cols] of a matrix with cols + 8 columns: strides (cols + 8, 1)
+        wide = rng.normal(size=(rows, cols + 8)).astype(np.float32)
+        wd, rd = dev(cuda, wide), dev(cuda, rowv)
+        out = cuda.empty((rows, cols), dtype=cuda.float32, device="cuda")
+        arr = C.c_int64 * 2
+        fdl.check(fdl.lib().fdl_broadcast_binary_f32(wd.data_ptr() + 16, rd.data_ptr(), out.data_ptr(), 2, arr(rows, cols),
+                                                     arr(cols + 8, 1), arr(0, 1), fdl.MUL, None), "window")
+        assert_bit_exact(to_np(out), wide[:, 4:4 + cols] * rowv, "window of a wider matrix")
+        # in place: the output is the dense operand
+        dd = dev(cuda, dense)
+        fdl.broadcast_binary(dd, dev(cuda, colv), fdl.MUL, out=dd)
+        assert_bit_exact(to_np(dd), dense * colv, "in place")
+    finally:
+        fdl.set_tuning("bcast2d_rows", 0)
+
+
+def test_two_dimensional_kernel_equals_general_kernel(fdl, cuda):
+    rng = np.random.default_rng(47)
+    a = dev(cuda, rng.normal(size=(513, 2052)).astype(np.float32))
+    for other in (rng.normal(size=(1, 2052)), rng.normal(size=(513, 1))):
+        b = dev(cuda, other.astype(np.float32))
+        fast = to_np(fdl.broadcast_binary(a, b, fdl.SUB))
+        fdl.set_tuning("bcast2d", 0)
+        try:
+            general = to_np(fdl.broadcast_binary(a, b, fdl.SUB))
+        finally:
+            fdl.set_tuning("bcast2d", 1)
+        assert_bit_exact(fast, general, "2-D kernel vs general kernel")
+
+
 def test_config2_bias_then_scale(fdl, cuda):
     """A[4096,4096] + b[1,4096], then * s[4096,1] (stride-0 indexing on either axis)."""
     rng = np.random.default_rng(44)

@@ -103,8 +103,25 @@ def _worker(rank, world, port, n, out):
             cols_ok &= good
         capi.take_device_error()
         dist.barrier()
+        final32 = o32.item()
+        # Last, a collective that one rank never joins: rank 1 stays alive but skips the call.
+        # Rank 0's kernel waits 50 ms for the missing partial, gives up, writes NaN and raises
+        # the device-error flag; an ordinary sum afterwards is correct.  (The contexts' epochs
+        # are out of step after this, so they are closed right away.)
+        timeout_ok = True
+        if rank == 0:
+            capi.set_tuning("exchange_wait_ms", 50)
+            ex.sum(x, o32, o64)
+            torch.cuda.synchronize()
+            timeout_ok = bool(np.isnan(o64.item())) and capi.lib().fdl_take_device_error() == -4 \
+                and capi.lib().fdl_take_device_error() == 0
+            timeout_ok &= capi.full_sum(x, want_f64=True)[1].item() == local64.item()
+            capi.set_tuning("exchange_wait_ms", 2000)
+            if not timeout_ok:
+                print("rank 0: the bounded wait did not report as expected", flush=True)
+        dist.barrier()
         ex.close()
-        sum_ok = all(r == want for r in results) and np.float32(want) == o32.item()
+        sum_ok = all(r == want for r in results) and np.float32(want) == final32 and timeout_ok
         if not sum_ok:
             print(f"rank {rank}: sum results {results} want {want}", flush=True)
         ok = sum_ok and cols_ok

@@ -51,6 +51,35 @@ def test_static_and_regular_calls_interleave(fdl, cuda):
     assert_sum_close(to_np(fdl.full_sum_static(unaligned))[0], rb, nb, "unaligned input")
 
 
+def test_no_device_memory_is_taken(fdl, cuda):
+    """The point of the entry point: the device's free memory is the same before the first
+    call, after it and after later calls (the regular entry point, in contrast, may allocate
+    the library's workspace on its first use)."""
+    x = cuda.ones(1 << 22, dtype=cuda.float32, device="cuda")
+    out = cuda.zeros(1, dtype=cuda.float32, device="cuda")
+    cuda.cuda.synchronize()
+    free_before, _ = cuda.cuda.mem_get_info()
+    for _ in range(3):
+        fdl.check(fdl.lib().fdl_sum_f32_static(x.data_ptr(), x.numel(), out.data_ptr(), None, None), "static sum")
+        cuda.cuda.synchronize()
+        free_now, _ = cuda.cuda.mem_get_info()
+        assert free_now == free_before
+    assert out.item() == float(1 << 22)
+
+
+def test_the_maximum_size_itself_is_accepted(fdl, cuda):
+    n = 1 << 30
+    free, _ = cuda.cuda.mem_get_info()
+    if free < n * 4 + (1 << 30):
+        pytest.skip("not enough free device memory for 2^30 floats")
+    x = cuda.full((n,), 0.25, dtype=cuda.float32, device="cuda")
+    for _ in range(2):
+        s32, s64 = fdl.full_sum_static(x, want_f64=True)
+        assert s64.item() == 0.25 * n and s32.item() == 0.25 * n   # exact in both widths
+    x[n - 1] = 1.25
+    assert fdl.full_sum_static(x, want_f64=True)[1].item() == 0.25 * n + 1.0
+
+
 def test_sizes_above_the_maximum_are_refused(fdl, cuda):
     x = cuda.zeros(16, dtype=cuda.float32, device="cuda")
     out = cuda.zeros(1, dtype=cuda.float32, device="cuda")
