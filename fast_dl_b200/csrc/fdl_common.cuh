@@ -48,6 +48,7 @@ struct Tuning {
     int cols_cluster = 4;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8)
     int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
     int cols_chunks = 0;         // column reduction: row chunks per column block (0 = derived)
+    int cols_single = 1;         // column reduction: prefer one cluster of 8 per column block where it fits
     int rows_cluster_threads = 256;  // cluster form of rows up to 65536 floats: threads per CTA (256 or 512)
     int rows_warp16 = -1;        // row softmax/layernorm: rows of 1028..2048 floats by one warp, 16 packs a
                                  // lane (1), by a 256-thread CTA (0), or whichever measured faster (-1)

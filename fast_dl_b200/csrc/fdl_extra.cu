@@ -18,19 +18,27 @@ __device__ __forceinline__ bool aligned16_dev(const void* p) {
 //
 // The reference walks each row with ONE thread, twice, and adds loss_i / batch into a single
 // float with atomicAdd (src/kernels/cuda/cross_entropy.cu:9-35): uncoalesced, two reads and
-// order-dependent.  Here a team of TPR lanes owns a row and reads it ONCE with 128-bit loads,
-// eight per lane in flight: every lane keeps a running (max, sum of exp) pair that is
-// rescaled when the maximum moves (the row statistics of softmax, computed online), the
-// pairs meet through shuffles, and lane 0 forms log(sum) + max - x[label].  Rows whose label
-// is out of range contribute 0, as in the reference (:17-19).  The batch mean is
-// deterministic: loss_i / batch goes to a scratch vector and the full sum (launched so that
-// its start overlaps this kernel's tail) folds that vector in a fixed order.  A form that
-// folded inside this kernel (a double per CTA, a ticket, the last CTA adding them) measured
-// 51 us on [65536, 1024] against the 41 us of its traffic: the fence and the ticket's round
-// trip keep every CTA resident for a microsecond in which it has no loads in flight.
+// order-dependent.  Here a team of TPR lanes owns a row and reads it ONCE with 128-bit loads:
+// every lane keeps a running (max, sum of exp) pair that is rescaled when the maximum moves
+// (the row statistics of softmax, computed online), the lanes' pairs meet through shuffles,
+// and lane 0 forms log(sum) + max - x[label].  Rows whose label is out of range contribute 0,
+// as in the reference (:17-19).
+//
+// With about twenty instructions per 128-bit pack -- four of them on the special-function
+// unit -- the kernel is as much bound by instruction issue as by memory, so the form with the
+// fewest instructions wins: one row per team, the row's packs loaded eight at a time by
+// unrolled code with one address computation, the maximum as a tree, four independent sums.
+// Forms that keep more loads in flight at the price of bookkeeping measured slower on
+// [65536, 1024]: two eight-pack buffers used in turn over four rows per team 50 us, a ring
+// of eight slots refilled one by one 56 us (80 instructions per pack, issue slots 77% busy).
+//
+// The batch mean is deterministic without float atomics and without a ticket: lane 0 adds its
+// rows' losses in row order, thread 0 adds the CTA's teams in team order into one double per
+// CTA, and a one-CTA kernel (launched so that its start overlaps this kernel's tail) folds the
+// CTAs' doubles in index order.
 
 constexpr int kCeThreads = 256;
-constexpr int kCeInFlight = 8;  // items (128-bit packs, or floats) a lane loads before it uses them
+constexpr int kCeInFlight = 8;  // items (128-bit packs, or floats) per lane and chunk
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float exp2_approx(float x) {
@@ -45,77 +53,109 @@ __device__ __forceinline__ float exp_diff(float a, float b) {
 }
 
 template <int TPR, bool VEC>
-__global__ void __launch_bounds__(kCeThreads, 6)
-cross_entropy_rows_kernel(const float* logits, const int64_t* labels, float* row_loss, int batch, int classes,
-                          float inv_batch) {
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_rows_kernel(const float* logits, const int64_t* labels, double* cta_loss, int batch, int classes) {
     constexpr int kTeams = kCeThreads / TPR;
+    constexpr int kW = VEC ? 4 : 1;
+    __shared__ float team_loss[kTeams];
     const int lane = threadIdx.x % TPR;
     const int team = threadIdx.x / TPR;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    const bool active = row < batch;
+    const int items = VEC ? classes / 4 : classes;
+    const float* x = logits + (active ? row : 0) * classes;
     pdl_wait();
-    float m = -INFINITY, s = 0.0f;
-    float picked = 0.0f;   // the logit of the row's label (lane 0), asked for before the row streams in
+    // Lane 0 asks for the label and its logit before the row streams in.
+    float picked = 0.0f;
     bool valid = false;
-    if (row < batch) {
-        const float* x = logits + row * classes;
-        if (lane == 0) {
-            const int64_t label = labels[row];
-            valid = label >= 0 && label < classes;
-            if (valid) picked = x[label];
-        }
-        const int items = VEC ? classes / 4 : classes;
-        for (int i0 = lane; i0 < items; i0 += TPR * kCeInFlight) {
-            float v[kCeInFlight][VEC ? 4 : 1];
-#pragma unroll
-            for (int u = 0; u < kCeInFlight; ++u) {
-                const int i = i0 + u * TPR;
-                if (VEC) {
-                    const float4 t = i < items ? ld_stream(reinterpret_cast<const float4*>(x) + i)
-                                               : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-                    v[u][0] = t.x; v[u][1 % (VEC ? 4 : 1)] = t.y; v[u][2 % (VEC ? 4 : 1)] = t.z; v[u][3 % (VEC ? 4 : 1)] = t.w;
-                } else {
-                    v[u][0] = i < items ? ld_stream(x + i) : -INFINITY;
-                }
-            }
-            float m_new = m;
-#pragma unroll
-            for (int u = 0; u < kCeInFlight; ++u) {
-#pragma unroll
-                for (int k = 0; k < (VEC ? 4 : 1); ++k) m_new = fmaxf(m_new, v[u][k]);
-            }
-            // (x - max) first: the difference of equal values is exactly 0 whatever their size,
-            // which x * log2e - max * log2e does not guarantee for huge logits.
-            float add = 0.0f;
-#pragma unroll
-            for (int u = 0; u < kCeInFlight; ++u) {
-#pragma unroll
-                for (int k = 0; k < (VEC ? 4 : 1); ++k) add += exp2_approx((v[u][k] - m_new) * kLog2e);
-            }
-            s = s * exp_diff(m, m_new) + add;
-            m = m_new;
-        }
+    if (lane == 0 && active) {
+        const int64_t label = labels[row];
+        valid = label >= 0 && label < classes;
+        if (valid) picked = x[label];
     }
-    pdl_trigger();
+    float m = -INFINITY, s = 0.0f;
+    for (int i0 = lane; i0 < items; i0 += TPR * kCeInFlight) {
+        float v[kCeInFlight][kW];
 #pragma unroll
-    for (int o = TPR / 2; o > 0; o >>= 1) {
-        const float mo = __shfl_xor_sync(kFullMask, m, o);
-        const float so = __shfl_xor_sync(kFullMask, s, o);
-        const float m_new = fmaxf(m, mo);
-        s = s * exp_diff(m, m_new) + so * exp_diff(mo, m_new);
+        for (int u = 0; u < kCeInFlight; ++u) {
+            const int i = i0 + u * TPR;
+            if (VEC) {
+                const float4 t = active && i < items ? ld_stream(reinterpret_cast<const float4*>(x) + i)
+                                                     : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                v[u][0] = t.x; v[u][1 % kW] = t.y; v[u][2 % kW] = t.z; v[u][3 % kW] = t.w;
+            } else {
+                v[u][0] = active && i < items ? ld_stream(x + i) : -INFINITY;
+            }
+        }
+        // maximum of the chunk as a tree, then one rescale of the running sum
+        float mx[kCeInFlight];
+#pragma unroll
+        for (int u = 0; u < kCeInFlight; ++u) {
+            mx[u] = v[u][0];
+#pragma unroll
+            for (int k = 1; k < kW; ++k) mx[u] = fmaxf(mx[u], v[u][k]);
+        }
+#pragma unroll
+        for (int o = kCeInFlight / 2; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < o; ++u) mx[u] = fmaxf(mx[u], mx[u + o]);
+        }
+        const float m_new = fmaxf(m, mx[0]);
+        // (x - max) first: the difference of equal values is exactly 0 whatever their size,
+        // which x * log2e - max * log2e does not guarantee for huge logits.
+        float add[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int u = 0; u < kCeInFlight; ++u) {
+#pragma unroll
+            for (int k = 0; k < kW; ++k) add[(u * kW + k) & 3] += exp2_approx((v[u][k] - m_new) * kLog2e);
+        }
+        s = s * exp_diff(m, m_new) + ((add[0] + add[1]) + (add[2] + add[3]));
         m = m_new;
     }
-    if (lane == 0 && row < batch) row_loss[row] = valid ? (logf(s) + m - picked) * inv_batch : 0.0f;
+    pdl_trigger();
+    // team maximum, every lane rescales its sum once, team sum
+    float big = m;
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(kFullMask, big, o));
+    float part = s * exp_diff(m, big);
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) part += __shfl_xor_sync(kFullMask, part, o);
+    if (lane == 0) team_loss[team] = valid ? logf(part) + big - picked : 0.0f;
+    __syncthreads();
+    // The CTA's rows in team order into one double; no fence, no ticket: the CTA is done.
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll 8
+        for (int k = 0; k < kTeams; ++k) t += static_cast<double>(team_loss[k]);
+        cta_loss[blockIdx.x] = t;
+    }
+}
+
+// One CTA folds the per-CTA losses in index order and writes the batch mean.
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_finish_kernel(const double* cta_loss, int n, float* loss, double inv_batch) {
+    __shared__ double red[kCeThreads];
+    pdl_wait();
+    double t = 0.0;
+    for (int k = threadIdx.x; k < n; k += kCeThreads) t += cta_loss[k];
+    red[threadIdx.x] = t;
+    __syncthreads();
+    for (int o = kCeThreads / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *loss = static_cast<float>(red[0] * inv_batch);
 }
 
 template <int TPR>
 int launch_cross_entropy(bool vec, unsigned int grid, cudaStream_t stream, const float* logits, const int64_t* labels,
-                         float* row_loss, int batch, int classes, float inv_batch) {
+                         double* cta_loss, int batch, int classes) {
     const bool pdl = tuning().pdl != 0;
     const dim3 g(grid), b(kCeThreads), one(1, 1, 1);
-    return vec ? launch_ex(cross_entropy_rows_kernel<TPR, true>, g, b, 0, stream, one, pdl, logits, labels, row_loss,
-                           batch, classes, inv_batch)
-               : launch_ex(cross_entropy_rows_kernel<TPR, false>, g, b, 0, stream, one, pdl, logits, labels, row_loss,
-                           batch, classes, inv_batch);
+    return vec ? launch_ex(cross_entropy_rows_kernel<TPR, true>, g, b, 0, stream, one, pdl, logits, labels, cta_loss,
+                           batch, classes)
+               : launch_ex(cross_entropy_rows_kernel<TPR, false>, g, b, 0, stream, one, pdl, logits, labels, cta_loss,
+                           batch, classes);
 }
 
 // ---- square transpose -------------------------------------------------------------------------------
@@ -228,8 +268,11 @@ __device__ __forceinline__ void philox4x32_10(uint64_t counter, const PhiloxKeys
 }
 
 // (0, 1]: never 0, so the logarithm below is safe; same open/closed ends as curand_uniform.
+// The top 23 bits become the mantissa of a float in [1, 2), which is subtracted from 2: two
+// integer operations and an add, where an integer-to-float conversion would go through the
+// quarter-rate conversion unit (it made the uniform fill conversion-bound).
 __device__ __forceinline__ float unit_open_closed(uint32_t w) {
-    return fmaf(static_cast<float>(w >> 8), 1.0f / 16777216.0f, 1.0f / 16777216.0f);
+    return 2.0f - __uint_as_float((w >> 9) | 0x3f800000u);
 }
 
 // Two quads of floats per thread: 128-bit stores, and two independent Philox chains to
@@ -250,7 +293,8 @@ random_fill_kernel(float* data, int64_t n, float p0, float p1, const __grid_cons
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
                 const float u1 = unit_open_closed(w[2 * k]), u2 = unit_open_closed(w[2 * k + 1]);
-                const float r = __fsqrt_rn(-1.3862943611198906f * __log2f(u1));  // sqrt(-2 ln u1)
+                float r;  // sqrt(-2 ln u1)
+                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * __log2f(u1)));
                 float sn, cs;
                 __sincosf(6.283185307179586f * u2, &sn, &cs);
                 v[q][2 * k] = fmaf(p1, r * cs, p0);
@@ -297,29 +341,28 @@ int fdl_cross_entropy_f32(const float* logits, const int64_t* labels, float* los
     if (batch == 0) return static_cast<int>(cudaMemsetAsync(loss, 0, sizeof(float), s));
     if (logits == nullptr || labels == nullptr) return FDL_ERR_INVALID_ARGUMENT;
     const bool vec = classes % 4 == 0 && aligned16(logits);
-    // A team of lanes per row: about eight items (packs on the 128-bit path) per lane.
+    // A team of lanes per row: about eight items (packs on the 128-bit path) per lane and chunk.
     const int64_t items = vec ? classes / 4 : classes;
     int tpr = 1;
     while (tpr < kWarp && static_cast<int64_t>(tpr) * kCeInFlight < items) tpr <<= 1;
     const int64_t grid = ceil_div(batch, kCeThreads / tpr);
-    const size_t sum_bytes = fdl_sum_scratch_bytes(batch);
     void* ws = nullptr;
-    int status = get_workspace(sum_bytes + static_cast<size_t>(batch) * sizeof(float) + 256, &ws);
+    int status = get_workspace(static_cast<size_t>(kWorkspaceCounterBytes) + static_cast<size_t>(grid) * sizeof(double), &ws);
     if (status != FDL_OK) return status;
-    float* row_loss = reinterpret_cast<float*>(static_cast<char*>(ws) + sum_bytes);
+    double* cta_loss = reinterpret_cast<double*>(static_cast<char*>(ws) + kWorkspaceCounterBytes);
     const unsigned int g = static_cast<unsigned int>(grid);
     const int b = static_cast<int>(batch), c = static_cast<int>(classes);
-    const float inv_batch = 1.0f / static_cast<float>(batch);
     switch (tpr) {
-        case 1: status = launch_cross_entropy<1>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
-        case 2: status = launch_cross_entropy<2>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
-        case 4: status = launch_cross_entropy<4>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
-        case 8: status = launch_cross_entropy<8>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
-        case 16: status = launch_cross_entropy<16>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
-        default: status = launch_cross_entropy<32>(vec, g, s, logits, labels, row_loss, b, c, inv_batch); break;
+        case 1: status = launch_cross_entropy<1>(vec, g, s, logits, labels, cta_loss, b, c); break;
+        case 2: status = launch_cross_entropy<2>(vec, g, s, logits, labels, cta_loss, b, c); break;
+        case 4: status = launch_cross_entropy<4>(vec, g, s, logits, labels, cta_loss, b, c); break;
+        case 8: status = launch_cross_entropy<8>(vec, g, s, logits, labels, cta_loss, b, c); break;
+        case 16: status = launch_cross_entropy<16>(vec, g, s, logits, labels, cta_loss, b, c); break;
+        default: status = launch_cross_entropy<32>(vec, g, s, logits, labels, cta_loss, b, c); break;
     }
     if (status != FDL_OK) return status;
-    return fdl_sum_f32(row_loss, batch, loss, nullptr, ws, sum_bytes, stream);
+    return launch_ex(cross_entropy_finish_kernel, dim3(1), dim3(kCeThreads), 0, s, dim3(1, 1, 1), tuning().pdl != 0,
+                     static_cast<const double*>(cta_loss), static_cast<int>(grid), loss, 1.0 / static_cast<double>(batch));
 }
 
 int fdl_transpose_f32(const float* in, float* out, int64_t n, void* stream) {

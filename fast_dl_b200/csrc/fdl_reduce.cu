@@ -660,12 +660,14 @@ reduce_rows_kernel(const float* x, int64_t rows, int cols, typename R::Out* out,
     const int t = threadIdx.x % TPR;        // position inside the row team
     const int team = threadIdx.x / TPR;
     const int npack = cols / W;
+    pdl_wait();  // the input may be the previous kernel's output
 
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + team; row < rows;
          row += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
         int head = 0;
         State s = W == 4 ? thread_reduce_span<R, 4, TPR>(x + row * cols, t, npack)
                          : thread_reduce_flat<R, TPR>(x, phase, row, cols, t, 0, INT_MAX, &head);
+        pdl_trigger();
 #pragma unroll
         for (int o = kWarp / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
         if (TPR == kWarp) {
@@ -935,9 +937,8 @@ int launch_rows_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out*
     int64_t grid = ceil_div(rows, kRowsPerCta);
     if (grid > 2147483647) grid = 2147483647;
     const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(x) & 15u) / 4u);
-    reduce_rows_kernel<R, TPR, W><<<static_cast<unsigned int>(grid), kRowThreads, 0, stream>>>(
-        x, rows, static_cast<int>(cols), out, static_cast<float>(cols), phase);
-    return launch_status();
+    return launch_ex(reduce_rows_kernel<R, TPR, W>, dim3(static_cast<unsigned int>(grid)), dim3(kRowThreads), 0, stream,
+                     dim3(1, 1, 1), tuning().pdl != 0, x, rows, static_cast<int>(cols), out, static_cast<float>(cols), phase);
 }
 
 template <class R>
@@ -1025,6 +1026,9 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
     const int64_t r_begin = static_cast<int64_t>(chunk) * rows_per_chunk;
     int64_t r_end = r_begin + rows_per_chunk;
     if (r_end > rows) r_end = rows;
+    pdl_wait();  // the input may be the previous kernel's output; the scratch was its scratch
+    // (A form that refills each of the eight slots as soon as it has been added, to keep
+    // requests outstanding during the adds, measured slower: 60 against 54 us on [2097152, 32].)
     if (col < cols) {
         const float* xc = xb + col;
         bool have[C];  // W = 1: which of the four columns exist (the last tile may be ragged)
@@ -1064,6 +1068,7 @@ reduce_cols_kernel(const float* x, int64_t rows, int64_t cols, float* out, float
             }
         }
     }
+    pdl_trigger();
 #pragma unroll
     for (int k = 0; k < C; ++k) {
         tile[ry * tile_w + (W == 4 ? cx * 4 + k : k * tx + cx)] = R::combine(acc[0][k], acc[1][k]);
@@ -1288,6 +1293,29 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
                   ColsGeometry* g) {
     g->w = vec ? 4 : 1;  // load width; a thread owns four columns either way
     const int64_t packs = ceil_div(cols, 4);
+    // Preferred shape: ONE cluster of eight CTAs covers all the rows of a column block, so the
+    // fold through distributed shared memory is the last stage -- no partials in global memory,
+    // no ticket, no second pass (on [8192, 8192] that tail is worth 4 of 49 us).  It is taken when
+    // a tile width of 32 to 256 threads gives between 2.5 and 5.5 CTAs per SM (all resident at
+    // once, a CTA lives as long as the kernel) and every thread row still gets 16 rows.
+    if (tuning().cols_single != 0 && tuning().cols_chunks == 0 && batch == 1) {
+        constexpr int kSingle = 8;
+        for (int tx = 32; tx <= kColThreads; tx <<= 1) {
+            const int64_t blocks = ceil_div(packs, tx);
+            const int64_t ctas = blocks * kSingle;
+            const int ty = kColThreads / tx;
+            if (ctas * 2 < static_cast<int64_t>(sm_count) * 5 || ctas * 2 > static_cast<int64_t>(sm_count) * 11) continue;
+            if (rows < static_cast<int64_t>(kSingle) * ty * 16 || ceil_div(rows, kSingle) > 2147483647) continue;
+            g->tx = tx;
+            g->col_blocks = static_cast<int>(blocks);
+            g->rows_per_chunk = static_cast<int>(ceil_div(rows, kSingle));
+            g->chunks = kSingle;
+            g->cluster = kSingle;
+            g->counter_bytes = kCounterBytes;
+            g->scratch_bytes = 0;
+            return FDL_OK;
+        }
+    }
     int tx = 1;
     int tx_max = tuning().cols_tx;  // threads across columns (x4 floats = row bytes per CTA)
     // With few rows, thread rows beyond rows / 8 would sit idle: widen the tile instead (a
@@ -1537,23 +1565,15 @@ static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t
         partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + g.counter_bytes);
     }
     const float scale = op == FDL_REDUCE_MEAN ? static_cast<float>(1.0 / mean_divisor) : 1.0f;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(g.col_blocks, g.chunks, static_cast<unsigned int>(batch));
-    cfg.blockDim = dim3(kColThreads);
-    cfg.dynamicSmemBytes = static_cast<size_t>(kColThreads) * 4 * sizeof(float);
-    cfg.stream = as_stream(stream);
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 1;
-    attr.val.clusterDim.y = g.cluster;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = g.cluster > 1 ? 1 : 0;
+    const dim3 grid(g.col_blocks, g.chunks, static_cast<unsigned int>(batch)), block(kColThreads), cluster(1, g.cluster, 1);
+    const size_t smem = static_cast<size_t>(kColThreads) * 4 * sizeof(float);
+    const bool pdl = tuning().pdl != 0;
+    cudaStream_t st = as_stream(stream);
     const bool is_max = op == FDL_REDUCE_MAX;
-    cudaError_t e;
-#define FDL_LAUNCH_COLS(R, W, CL)                                                              \
-    e = cudaLaunchKernelEx(&cfg, reduce_cols_kernel<R, W, CL>, x, rows, cols, out, partials,  \
-                           counters, g.tx, g.rows_per_chunk, scale, xc)
+    int launched = FDL_OK;
+#define FDL_LAUNCH_COLS(R, W, CL)                                                                           \
+    launched = launch_ex(reduce_cols_kernel<R, W, CL>, grid, block, smem, st, cluster, pdl, x, rows, cols, out, \
+                         partials, counters, g.tx, g.rows_per_chunk, scale, xc)
 #define FDL_LAUNCH_COLS_CL(CL)                                                                  \
     do {                                                                                        \
         if (is_max) { if (vec) FDL_LAUNCH_COLS(ColMax, 4, CL); else FDL_LAUNCH_COLS(ColMax, 1, CL); } \
@@ -1575,8 +1595,7 @@ static int reduce_cols_impl(const float* x, int64_t batch, int64_t rows, int64_t
     }
 #undef FDL_LAUNCH_COLS_CL
 #undef FDL_LAUNCH_COLS
-    if (e != cudaSuccess) return static_cast<int>(e);
-    return launch_status();
+    return launched;
 }
 
 int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t cols, float* out,

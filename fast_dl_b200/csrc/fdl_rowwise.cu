@@ -230,12 +230,14 @@ rows_direct_kernel(const RowParams p) {
     const int nvec = p.cols / 4;
     const float4* src = reinterpret_cast<const float4*>(p.x + (active ? row : 0) * p.cols);
     float4 v[NV];
+    pdl_wait();  // the input may be the previous kernel's output
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (t + i * TPR < nvec) {
             v[i] = active ? ld_stream(src + t + i * TPR) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
+    pdl_trigger();  // the row is on its way: the next kernel of the stream may be scheduled
     TeamScope<TPR, TH> scope{red};
     row_math<TPR, TH, NV>(Op{}, v, t, nvec, p, row, active, scope);
 }
@@ -1044,8 +1046,8 @@ int launch_direct_cfg(const RowParams& p, const DeviceInfo*, cudaStream_t stream
     constexpr int kTeams = TH / TPR;
     const int64_t grid = ceil_div(p.rows, kTeams);
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
-    rows_direct_kernel<Op, TPR, TH, NV><<<static_cast<unsigned int>(grid), TH, 0, stream>>>(p);
-    return launch_status();
+    return launch_ex(rows_direct_kernel<Op, TPR, TH, NV>, dim3(static_cast<unsigned int>(grid)), dim3(TH), 0, stream,
+                     dim3(1, 1, 1), tuning().pdl != 0, p);
 }
 
 template <class Op, int TPR, int TH, int NV>

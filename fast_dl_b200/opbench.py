@@ -391,8 +391,115 @@ def main_sharded() -> None:
         dist.destroy_process_group()
 
 
+def main_sum_trace() -> None:
+    """Where the time of the fused full sum + exchange goes, per rank.
+
+        python -m torch.distributed.run --nproc-per-node N -m fast_dl_b200.opbench --sum-trace [--json out.json]
+
+    Every rank runs the large-sweep step (add, broadcast add, full sum with the exchange in the
+    kernel) on its shard of 2^28 / N elements, `--steps` steps back to back, `--reps` times.  With
+    the tuning key "sum_trace" set, the CTA that finishes the last sum of a repetition leaves
+    %globaltimer stamps; the table gives, per rank, the mean time from the kernel's start to the
+    last cluster's ticket (the streaming part), from there to the folded partial, to the peer
+    stores, to the moment all peers' partials have been seen (NVLink latency + the skew between
+    ranks that the exchange absorbs) and to the written result.
+    """
+    import os
+
+    import torch
+    import torch.distributed as dist
+    from fast_dl_b200 import capi
+    from fast_dl_b200.sharding import shard_rows
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sum-trace", action="store_true")
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--tune", action="append", default=[])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    capi.lib()
+    capi.use_device(local)
+    for kv in args.tune:
+        k, v = kv.split("=")
+        capi.set_tuning(k, int(v))
+    dev = torch.device("cuda", local)
+    exchange = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+        def gather(handle):
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            return handles
+        exchange = capi.Exchange(world, rank, gather)
+        dist.barrier()
+    R = C = 16384
+    r = shard_rows(R, world, rank).count
+    gen = torch.Generator(device=dev).manual_seed(42 + rank)
+    a, b, d, f = (torch.empty(r * C, dtype=torch.float32, device=dev).uniform_(-1, 1, generator=gen) for _ in range(4))
+    c, e = torch.empty_like(a), torch.empty_like(a)
+    row = torch.empty((1, C), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=gen)
+    s32 = torch.zeros(1, dtype=torch.float32, device=dev)
+    s64 = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    def step():
+        capi.binary(a, b, capi.ADD, out=c)
+        capi.broadcast_binary(d.view(r, C), row, capi.ADD, out=e.view(r, C))
+        if exchange is not None:
+            exchange.sum(f, s32, s64)
+        else:
+            capi.full_sum(f)
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    capi.set_tuning("sum_trace", 1)
+    names = ["stream_us", "fold_us", "send_us", "wait_peers_us", "write_us", "tail_cycles"]
+    rows = []
+    for _ in range(args.reps):
+        if world > 1:
+            dist.barrier()
+        for _ in range(args.steps):
+            step()
+        torch.cuda.synchronize()
+        w = capi.sum_trace()
+        t_fold_end = w[2]
+        sent = w[3] if exchange is not None else t_fold_end
+        seen = w[4] if exchange is not None else sent
+        rows.append([(w[1] - w[0]) / 1e3, (w[2] - w[1]) / 1e3, (sent - t_fold_end) / 1e3, (seen - sent) / 1e3,
+                     (w[5] - seen) / 1e3, float(w[6])])
+    capi.set_tuning("sum_trace", 0)
+    mean = [statistics.mean(col) for col in zip(*rows)]
+    med = [statistics.median(col) for col in zip(*rows)]
+    mine = {"rank": rank, "mean": dict(zip(names, mean)), "median": dict(zip(names, med))}
+    everyone = [mine]
+    if world > 1:
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+    if rank == 0:
+        print(f"full sum + exchange on {world} GPU(s), shard {r * C} elements; median over {args.reps} repetitions")
+        print("rank  " + "  ".join(f"{n:>14s}" for n in names))
+        for rec in everyone:
+            print(f"{rec['rank']:4d}  " + "  ".join(f"{rec['median'][n]:14.2f}" for n in names))
+        if args.json:
+            Path(args.json).write_text(json.dumps({"n_gpus": world, "ranks": everyone}, indent=1))
+    torch.cuda.synchronize()
+    capi.take_device_error()
+    if world > 1:
+        dist.barrier()
+        exchange.close()
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
-    if "--sharded" in sys.argv:
+    if "--sum-trace" in sys.argv:
+        main_sum_trace()
+    elif "--sharded" in sys.argv:
         main_sharded()
     else:
         main()

@@ -111,7 +111,9 @@ int fdl_take_device_error(void);
  * (256 or 512 threads per CTA in the cluster form of rows of 16388..65536 floats; default 256),
  * and for the column reductions "cols_tx" (threads across columns per CTA: 16..256; default
  * 64), "cols_cluster" (1, 2, 4, 8, 16; default 4), "cols_ctas_per_sm" (default 4) and
- * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default);
+ * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default),
+ * "cols_single" (1 = where the shape allows, one cluster of 8 CTAs covers all rows of a column
+ * block and nothing goes through scratch; 0 = always the chunked form; default 1);
  * "pdl" (1 = the streaming kernels are launched with programmatic stream serialization, so
  * that the next kernel's launch overlaps the tail of the one before; 0 = plain launches;
  * default 1), "bcast2d" (1 = two-dimensional broadcasts take the division-free kernel;
@@ -363,7 +365,10 @@ int fdl_normal_f32(float* data, int64_t n, float mean, float stddev, uint64_t se
  * (include/dl/tensor/Tensor.hpp:97-121, src/tensor/TensorImpl.cpp:91-125) for callers
  * whose tensors live on the host.  Buffers should be page-locked (pageable memory works
  * but serialises the copies).  Staging memory (4 slots x 128 MiB per device) is allocated
- * on first use and kept. */
+ * on first use and kept.  The calls on one device share that ring: each holds the device's
+ * lock from start to finish, so concurrent callers on the same device run one after another
+ * (different devices are independent).  Whatever a call returns, every copy it enqueued has
+ * finished by then: the host buffers may be released at once. */
 int fdl_host_binary_f32(const float* h_a, const float* h_b, float* h_out, int64_t n, int op);
 int fdl_host_unary_f32(const float* h_x, float* h_out, int64_t n, int op, float alpha);
 int fdl_host_mul_add_relu_f32(const float* h_a, const float* h_b, const float* h_c,
