@@ -282,12 +282,14 @@ __device__ __forceinline__ float unit_open_closed(uint32_t w) {
 template <bool NORMAL>
 __global__ void __launch_bounds__(256)
 random_fill_kernel(float* data, int64_t n, float p0, float p1, const __grid_constant__ PhiloxKeys keys) {
-    const int64_t first = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) * 2;  // first of the thread's two quads
+    // The thread's two quads lie 256 quads apart, so that the 32 lanes of a warp store one
+    // contiguous 512-byte run per instruction.
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * 512 + threadIdx.x;
     float v[2][4];
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
         uint32_t w[4];
-        philox4x32_10(static_cast<uint64_t>(first + q), keys, w);
+        philox4x32_10(static_cast<uint64_t>(first + q * 256), keys, w);
         if (NORMAL) {
             // p0 = mean, p1 = stddev.
 #pragma unroll
@@ -313,9 +315,10 @@ random_fill_kernel(float* data, int64_t n, float p0, float p1, const __grid_cons
     const bool vec = aligned16_dev(data);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-        const int64_t base = (first + q) * 4;
+        const int64_t quad = first + q * 256;
+        const int64_t base = quad * 4;
         if (base + 3 < n && vec) {
-            st_stream(reinterpret_cast<float4*>(data) + first + q, make_float4(v[q][0], v[q][1], v[q][2], v[q][3]));
+            st_stream(reinterpret_cast<float4*>(data) + quad, make_float4(v[q][0], v[q][1], v[q][2], v[q][3]));
         } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {

@@ -127,7 +127,7 @@ int get_workspace(size_t bytes, void** out) {
 
 extern "C" {
 
-int fdl_version(void) { return 1000; }
+int fdl_version(void) { return 1001; }
 
 const char* fdl_error_string(int status) {
     switch (status) {
