@@ -53,7 +53,7 @@ __device__ __forceinline__ float exp_diff(float a, float b) {
 }
 
 template <int TPR, bool VEC>
-__global__ void __launch_bounds__(kCeThreads)
+__global__ void __launch_bounds__(kCeThreads, 5)
 cross_entropy_rows_kernel(const float* logits, const int64_t* labels, double* cta_loss, int batch, int classes) {
     constexpr int kTeams = kCeThreads / TPR;
     constexpr int kW = VEC ? 4 : 1;
@@ -268,11 +268,11 @@ __device__ __forceinline__ void philox4x32_10(uint64_t counter, const PhiloxKeys
 }
 
 // (0, 1]: never 0, so the logarithm below is safe; same open/closed ends as curand_uniform.
-// The top 23 bits become the mantissa of a float in [1, 2), which is subtracted from 2: two
-// integer operations and an add, where an integer-to-float conversion would go through the
-// quarter-rate conversion unit (it made the uniform fill conversion-bound).
+// Twenty-three bits of the word become the mantissa of a float in [1, 2), which is subtracted
+// from 2: one logic operation and an add, where an integer-to-float conversion would go
+// through the quarter-rate conversion unit (it made the uniform fill conversion-bound).
 __device__ __forceinline__ float unit_open_closed(uint32_t w) {
-    return 2.0f - __uint_as_float((w >> 9) | 0x3f800000u);
+    return 2.0f - __uint_as_float((w & 0x007fffffu) | 0x3f800000u);
 }
 
 // Two quads of floats per thread: 128-bit stores, and two independent Philox chains to

@@ -178,6 +178,50 @@ def test_column_reduction_batched_few_rows_and_many_chunks(fdl, cuda):
         assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "same bits")
 
 
+@pytest.mark.parametrize("rows,cols", [(16384, 4), (20000, 8), (1 << 17, 16), (300001, 32), (65536 + 7, 64), (40000, 128),
+                                       (1 << 21, 32)])
+def test_column_reduction_of_tall_narrow_matrices(fdl, cuda, rows, cols):
+    """Rows of 4 ... 128 floats: a single column block, hundreds of row chunks, the last CTA
+    folding them; with the library's and with the caller's scratch, twice in a row (the arrival
+    counters must come back to zero), and the full sum on the same workspace afterwards."""
+    rng = np.random.default_rng(rows + cols)
+    x = rng.normal(size=(rows, cols)).astype(np.float32)
+    x[rows // 2, cols - 1] = 1e6   # a lone large value must land in its own column
+    xd = dev(cuda, x)
+    x64 = x.astype(np.float64)
+    norm = np.sqrt((x64 ** 2).sum(axis=0))
+    nbytes = fdl.lib().fdl_reduce_cols_scratch_bytes(1, rows, cols)
+    scratch = cuda.zeros(max(nbytes, 256), dtype=cuda.uint8, device="cuda")
+    for use in (None, scratch, None):
+        assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM, scratch=use)), x64.sum(axis=0), norm, "col sum")
+        assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN, scratch=use)), x64.mean(axis=0), norm / rows, "col mean")
+        assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX, scratch=use)), x.max(axis=0), "col max")
+    assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "deterministic")
+    assert_sum_close(to_np(fdl.full_sum(xd))[0], x64.sum(), np.sqrt((x64 ** 2).sum()), "full sum afterwards")
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 8192), (4096, 8192), (5000, 12288), (2048, 16384), (3000, 32768), (1100, 65536)])
+def test_column_reduction_one_cluster_per_column_block(fdl, cuda, rows, cols):
+    """Shapes that take the form in which one cluster of eight CTAs covers all rows of a column
+    block (no scratch): against numpy in fp64 and against the chunked form (cols_single = 0)."""
+    rng = np.random.default_rng(cols)
+    x = rng.standard_normal((rows, cols), dtype=np.float32)
+    xd = dev(cuda, x)
+    x64 = x.astype(np.float64)
+    norm = np.sqrt((x64 ** 2).sum(axis=0))
+    single = to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM))
+    assert_sum_close(single, x64.sum(axis=0), norm, "col sum")
+    assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MEAN)), x64.mean(axis=0), norm / rows, "col mean")
+    assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX)), x.max(axis=0), "col max")
+    assert_bit_exact(single, to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "deterministic")
+    fdl.set_tuning("cols_single", 0)
+    try:
+        chunked = to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM))
+    finally:
+        fdl.set_tuning("cols_single", 1)
+    assert_sum_close(single, chunked, norm, "single cluster vs chunked")
+
+
 def test_config3_shapes(fdl, cuda):
     """X[8192,8192] ~ N(0,1): sum/max axis 1, mean axis 0, argmax axis 1, full sum."""
     rng = np.random.default_rng(42)
