@@ -54,6 +54,10 @@ struct Tuning {
                                  // lane (1), by a 256-thread CTA (0), or whichever measured faster (-1)
     int rows_staged = -1;  // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA,
                            // -1 = staged for rows of up to 128 floats, direct beyond
+    int rows_smem = 1;     // row softmax/layernorm: long rows in a cluster's shared memory, read once (0 = the
+                           // register-cluster and two-kernel forms)
+    int rows_smem_from = 0;     // aligned rows longer than this many floats take that form (0 = 65536)
+    int rows_smem_cluster = 0;  // CTAs per row in that form: 2, 4, 8, 16 (0 = by row length)
     int pdl = 1;           // streaming kernels are launched with programmatic stream serialization: the
                            // next kernel's launch and ramp-up overlap this one's tail (0 = plain launches)
     int exchange_wait_ms = 2000;  // how long a cross-GPU exchange waits for its peers before giving up

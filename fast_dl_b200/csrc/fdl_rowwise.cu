@@ -684,6 +684,254 @@ int launch_cluster_cfg(const RowParams& p, cudaStream_t stream) {
     return launch_status();
 }
 
+// ---- shared-memory cluster form: long rows at any phase, read once ------------------------------
+//
+// Beyond what a cluster's registers hold (and from 16384 floats on when the row length is not a
+// multiple of 4), a cluster of CL CTAs keeps the row in SHARED memory: the row's aligned packs
+// are cut into CL slices, thread 0 of each CTA asks the copy engine for its slice (bulk-async
+// copies on an mbarrier: the whole slice is in flight without occupying a register), the CTA
+// takes the slice's statistics from shared memory, ONE exchange of (maximum, sum of exp) or
+// (mean, squared deviations) pairs crosses the cluster through distributed shared memory as
+// in the register form, and the slice is normalised out of shared memory.  One read and one
+// write per element, where the two-kernel form reads twice.  Slices of up to 64 KiB leave room
+// for three or more CTAs per SM, so one CTA's arithmetic overlaps its neighbours' copies.  A
+// row may start at any phase of a 16-byte line: the first and last pack of a row are then
+// shared with the neighbouring rows; they are copied whole, read with the foreign lanes masked,
+// and written back one valid float at a time.  x and y must sit at the same phase.
+// A copy that does not complete in the bounded wait raises the device-error flag; the CTA then
+// still walks through the cluster barriers (its peers wait there) and stores nothing.
+
+template <class Op, int CL, int TH>
+__global__ void __launch_bounds__(TH)
+rows_smem_kernel(const RowParams p, int phase, int slice_pk) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float4* slice = reinterpret_cast<float4*>(smem_raw);
+    __shared__ uint64_t bar;
+    __shared__ float red[kMaxWarps];
+    __shared__ float slots[2][16];
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.barrier_arrive();  // waited for once the copy has been requested
+    const int64_t row = blockIdx.x / CL;
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int t = threadIdx.x;
+    const int64_t e0 = phase + row * p.cols;  // the row's first float, counted from the 16-byte line of x[0]
+    RowEdges edge;
+    edge.head = static_cast<int>(e0 & 3);
+    edge.cols = p.cols;
+    edge.npk = (edge.head + p.cols + 3) >> 2;
+    const int pk0 = rank * slice_pk;
+    int local = edge.npk - pk0;
+    local = local > slice_pk ? slice_pk : (local < 0 ? 0 : local);
+    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + pk0;
+    float4* dst = reinterpret_cast<float4*>(p.y - phase) + (e0 >> 2) + pk0;
+    // floats of the row in slice k (the same arithmetic on every CTA)
+    auto count_of = [&](int k) {
+        int lo = 4 * k * slice_pk, hi = lo + 4 * slice_pk;
+        lo = lo < edge.head ? edge.head : lo;
+        hi = hi > edge.head + p.cols ? edge.head + p.cols : hi;
+        return hi > lo ? hi - lo : 0;
+    };
+
+    if (t == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_wait();  // the input may be the previous kernel's output
+    if (t == 0 && local > 0) {
+        mbar_expect_tx(&bar, static_cast<uint32_t>(local) * 16u);
+        constexpr int kChunk = 4096;  // packs per copy (64 KiB)
+        for (int off = 0; off < local; off += kChunk) {
+            const int n = local - off < kChunk ? local - off : kChunk;
+            bulk_g2s(slice + off, src + off, static_cast<uint32_t>(n) * 16u, &bar);
+        }
+    }
+    cluster.barrier_wait();
+    bool landed = local == 0 || mbar_wait_bounded(&bar, 0);
+    landed = __syncthreads_and(landed);
+    pdl_trigger();
+    if (!landed && t == 0) atomicOr(p.error_flag, 1u);
+
+    // the packs of the row that this row owns only in part: at most the first and the last
+    const bool ragged = edge.head != 0 || ((edge.head + p.cols) & 3) != 0;
+    auto mask_of = [&](int i) { return ragged ? edge.valid(pk0 + i) : 15; };
+
+    // ---- this CTA's slice on its own ----
+    float a = kSoftmax ? -INFINITY : 0.0f;
+    if (landed) {
+        for (int i = t; i < local; i += TH) {
+            float4 v = slice[i];
+            const int ok = mask_of(i);
+            if (ok != 15) {
+                const float neutral = kSoftmax ? -INFINITY : 0.0f;
+                if (!(ok & 1)) v.x = neutral;
+                if (!(ok & 2)) v.y = neutral;
+                if (!(ok & 4)) v.z = neutral;
+                if (!(ok & 8)) v.w = neutral;
+            }
+            if (kSoftmax) a = fmaxf(a, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+            else a += (v.x + v.y) + (v.z + v.w);
+        }
+    }
+    const int mine = count_of(rank);
+    if (kSoftmax) a = team_max<TH, TH>(a, red);
+    else a = mine > 0 ? team_sum<TH, TH>(a, red) / static_cast<float>(mine) : team_sum<TH, TH>(a, red);
+    float b = 0.0f;
+    if (landed) {
+        for (int i = t; i < local; i += TH) {
+            float4 v = slice[i];
+            const int ok = mask_of(i);
+            if (kSoftmax) {
+                v.x = (ok & 1) ? fast_exp2((v.x - a) * kLog2e) : 0.0f;
+                v.y = (ok & 2) ? fast_exp2((v.y - a) * kLog2e) : 0.0f;
+                v.z = (ok & 4) ? fast_exp2((v.z - a) * kLog2e) : 0.0f;
+                v.w = (ok & 8) ? fast_exp2((v.w - a) * kLog2e) : 0.0f;
+                slice[i] = v;  // the exponentials replace the inputs
+                b += (v.x + v.y) + (v.z + v.w);
+            } else {
+                const float dx = (ok & 1) ? v.x - a : 0.0f, dy = (ok & 2) ? v.y - a : 0.0f;
+                const float dz = (ok & 4) ? v.z - a : 0.0f, dw = (ok & 8) ? v.w - a : 0.0f;
+                b += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+            }
+        }
+    }
+    b = team_sum<TH, TH>(b, red);
+    // ---- exchange through distributed shared memory ----
+    if (t == 0) {
+#pragma unroll
+        for (int k = 0; k < CL; ++k) {
+            float* peer = cluster.map_shared_rank(&slots[0][0], k);
+            peer[rank] = a;
+            peer[16 + rank] = b;
+        }
+    }
+    cluster.sync();
+    if (!landed) return;
+    // Writes a pack: whole when the row owns all of it, else its valid floats one by one.
+    auto store_pack = [&](int i, float4 o) {
+        const int ok = mask_of(i);
+        if (ok == 15) {
+            st_stream(dst + i, o);
+        } else {
+            float* q = reinterpret_cast<float*>(dst + i);
+            if (ok & 1) q[0] = o.x;
+            if (ok & 2) q[1] = o.y;
+            if (ok & 4) q[2] = o.z;
+            if (ok & 8) q[3] = o.w;
+        }
+    };
+    if (kSoftmax) {
+        float m = slots[0][0];
+#pragma unroll
+        for (int k = 1; k < CL; ++k) m = fmaxf(m, slots[0][k]);
+        float ssum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < CL; ++k) {
+            // a slice without a float of the row reports (-inf, 0)
+            ssum += slots[0][k] == -INFINITY ? 0.0f : slots[1][k] * fast_exp2((slots[0][k] - m) * kLog2e);
+        }
+        const float f = fast_exp2((a - m) * kLog2e) / ssum;
+        for (int i = t; i < local; i += TH) {
+            const float4 v = slice[i];
+            store_pack(i, make_float4(v.x * f, v.y * f, v.z * f, v.w * f));
+        }
+    } else {
+        const float inv_n = 1.0f / static_cast<float>(p.cols);
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < CL; ++k) sum += static_cast<float>(count_of(k)) * slots[0][k];
+        const float mean = sum * inv_n;
+        float m2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < CL; ++k) {
+            const float d = slots[0][k] - mean;
+            m2 += slots[1][k] + static_cast<float>(count_of(k)) * d * d;
+        }
+        const float rstd = 1.0f / sqrtf(m2 * inv_n + p.eps);
+        if (t == 0 && rank == 0) {
+            if (p.mean_out != nullptr) p.mean_out[row] = mean;
+            if (p.rstd_out != nullptr) p.rstd_out[row] = rstd;
+        }
+        const bool affine = p.gamma != nullptr || p.beta != nullptr;
+        for (int i = t; i < local; i += TH) {
+            const float4 v = slice[i];
+            float4 o = make_float4((v.x - mean) * rstd, (v.y - mean) * rstd, (v.z - mean) * rstd, (v.w - mean) * rstd);
+            if (affine) {
+                const int ok = mask_of(i);
+                const int c0 = 4 * (pk0 + i) - edge.head;  // column of the pack's first lane
+                float* lanes[4] = {&o.x, &o.y, &o.z, &o.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (ok & (1 << k)) {
+                        if (p.gamma != nullptr) *lanes[k] *= __ldg(p.gamma + c0 + k);
+                        if (p.beta != nullptr) *lanes[k] += __ldg(p.beta + c0 + k);
+                    }
+                }
+            }
+            store_pack(i, o);
+        }
+    }
+}
+
+// Packs per slice that one CTA may hold (dynamic shared memory, a little kept for the static part).
+inline int smem_slice_limit_packs(const DeviceInfo* info) { return (info->max_smem_optin - 2048) / 16; }
+
+template <class Op, int CL, int TH>
+int launch_rows_smem_cfg(const RowParams& p, const DeviceInfo* info, int phase, int slice_pk, cudaStream_t stream) {
+    auto kernel = rows_smem_kernel<Op, CL, TH>;
+    const size_t smem = static_cast<size_t>(slice_pk) * 16;
+    static size_t configured_smem[kMaxDevicesTracked] = {};
+    static bool nonportable[kMaxDevicesTracked] = {};
+    size_t& configured = configured_smem[info->device % kMaxDevicesTracked];
+    if (smem > 48 * 1024 - 1024 && smem > configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = smem;
+    }
+    if (CL > 8 && !nonportable[info->device % kMaxDevicesTracked]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        nonportable[info->device % kMaxDevicesTracked] = true;
+    }
+    return launch_ex(kernel, dim3(static_cast<unsigned int>(p.rows * CL)), dim3(TH), smem, stream, dim3(CL, 1, 1),
+                     tuning().pdl != 0, p, phase, slice_pk);
+}
+
+// Picks the cluster size (tuning key rows_smem_cluster forces one): the smallest of 2, 4, 8 CTAs
+// per row whose slices stay within `kSmemSliceTarget` packs, so that several CTAs fit an SM and one
+// CTA's arithmetic overlaps its neighbours' copies; FDL_ERR_UNSUPPORTED when even 16 CTAs (beyond
+// the portable cluster size) would need larger slices than one CTA's shared memory.
+constexpr int kSmemSliceTarget = 4096;  // 64 KiB
+
+template <class Op, int CL>
+int launch_rows_smem_cl(const RowParams& p, const DeviceInfo* info, int phase, int64_t npk_worst, cudaStream_t stream) {
+    const int64_t slice = ceil_div(npk_worst, CL);
+    if (slice > smem_slice_limit_packs(info)) return FDL_ERR_UNSUPPORTED;
+    if (slice <= kSmemSliceTarget) return launch_rows_smem_cfg<Op, CL, 256>(p, info, phase, static_cast<int>(slice), stream);
+    return launch_rows_smem_cfg<Op, CL, 512>(p, info, phase, static_cast<int>(slice), stream);
+}
+
+template <class Op>
+int launch_rows_smem(const RowParams& p, const DeviceInfo* info, cudaStream_t stream) {
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
+    const int64_t npk_worst = (static_cast<int64_t>(p.cols) + 6) / 4;  // a row at the worst phase
+    if (p.rows * 16 > 2147483647) return FDL_ERR_UNSUPPORTED;
+    int cl = tuning().rows_smem_cluster;
+    if (cl == 0) {
+        cl = 2;
+        while (cl < 8 && ceil_div(npk_worst, cl) > kSmemSliceTarget) cl <<= 1;
+        if (ceil_div(npk_worst, cl) > kSmemSliceTarget) return FDL_ERR_UNSUPPORTED;  // longer rows: the two-kernel form
+    }
+    switch (cl) {
+        case 2: return launch_rows_smem_cl<Op, 2>(p, info, phase, npk_worst, stream);
+        case 4: return launch_rows_smem_cl<Op, 4>(p, info, phase, npk_worst, stream);
+        case 8: return launch_rows_smem_cl<Op, 8>(p, info, phase, npk_worst, stream);
+        default: return launch_rows_smem_cl<Op, 16>(p, info, phase, npk_worst, stream);
+    }
+}
+
 // ---- staged form -------------------------------------------------------------------------------
 
 template <class Op, int TPR, int TH, int NV>
@@ -1132,6 +1380,14 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
                        (p.gamma == nullptr || aligned16(p.gamma)) &&
                        (p.beta == nullptr || aligned16(p.beta));
     constexpr int kCtaMaxCols = kClusterThreads * kClusterNV * 4;  // 16384 floats in one CTA's registers
+    const bool same_phase = ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0;
+    // Rows beyond 65536 floats (beyond 16384 when they do not consist of whole aligned packs):
+    // the row in a cluster's shared memory, read once.
+    const int smem_from = tuning().rows_smem_from > 0 ? tuning().rows_smem_from : 4 * kCtaMaxCols;
+    if (tuning().rows_smem != 0 && same_phase && (packs ? p.cols > smem_from : p.cols + 6 > kCtaMaxCols)) {
+        const int st = launch_rows_smem<Op>(p, info, stream);
+        if (st != FDL_ERR_UNSUPPORTED) return st;
+    }
     if (packs && p.cols > kCtaMaxCols && p.cols <= 8 * kCtaMaxCols) {
         if (tuning().rows_cluster_threads == 256 && p.cols <= 4 * kCtaMaxCols) {
             // 256-thread CTAs hold 8192 floats each: twice the CTAs per row, four resident per SM

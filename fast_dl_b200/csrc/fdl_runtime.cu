@@ -195,6 +195,18 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().rows_staged = value;
         return FDL_OK;
     }
+    if (k == "rows_smem_cluster" && (value == 0 || value == 2 || value == 4 || value == 8 || value == 16)) {
+        fdl::tuning().rows_smem_cluster = value;
+        return FDL_OK;
+    }
+    if (k == "rows_smem_from" && value >= 0) {
+        fdl::tuning().rows_smem_from = value;
+        return FDL_OK;
+    }
+    if (k == "rows_smem" && (value == 0 || value == 1)) {
+        fdl::tuning().rows_smem = value;
+        return FDL_OK;
+    }
     if (k == "pdl" && (value == 0 || value == 1)) {
         fdl::tuning().pdl = value;
         return FDL_OK;

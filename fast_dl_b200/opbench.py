@@ -184,7 +184,7 @@ def main(ref=None) -> None:
 
     if "rows" in cfgs:  # extra row-wise shapes: short and long rows
         for R, C in ((1 << 21, 32), (1 << 20, 64), (1 << 19, 128), (1 << 18, 256), (1 << 15, 2048), (1 << 14, 4096), (8192, 8192), (4096, 16384),
-                     (2048, 32768), (1024, 65536), (512, 131072), (128, 524288)):
+                     (2048, 32768), (1024, 65536), (512, 131072), (256, 262144), (128, 524288)):
             L = normal((R, C), 3.0)
             out = torch.empty_like(L)
             record("row", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))
@@ -223,7 +223,7 @@ def main(ref=None) -> None:
         del X, out
 
     if "odd" in cfgs:  # row lengths that are not a multiple of 4 floats: every row at another phase of a 16-byte line
-        for R, C in ((65536, 1001), (65536, 1023), (8192, 50257), (4096, 8191), (1 << 20, 63), (262144, 255)):
+        for R, C in ((65536, 1001), (65536, 1023), (8192, 50257), (4096, 8191), (1 << 20, 63), (262144, 255), (2048, 100003)):
             L = normal((R, C), 3.0)
             out = torch.empty_like(L)
             record("odd", f"softmax [{R},{C}]", 8 * R * C, lambda: capi.softmax_rows(L, out=out))

@@ -109,6 +109,10 @@ int fdl_take_device_error(void);
  * 1028..2048 floats: 1 = one warp per row with 16 packs a lane, 0 = a 256-thread CTA per row,
  * -1 = whichever measured faster for the op and length; default -1), "rows_cluster_threads"
  * (256 or 512 threads per CTA in the cluster form of rows of 16388..65536 floats; default 256),
+ * "rows_smem" (1 = rows beyond 65536 floats, or beyond 16384 at odd lengths, are kept in a
+ * cluster's shared memory and read once; 0 = the register-cluster and two-kernel forms; default 1),
+ * "rows_smem_cluster" (CTAs per row in that form: 2, 4, 8, 16, or 0 = by row length; default 0),
+ * "rows_smem_from" (aligned rows longer than this many floats take that form; 0 = 65536, default),
  * and for the column reductions "cols_tx" (threads across columns per CTA: 16..256; default
  * 64), "cols_cluster" (1, 2, 4, 8, 16; default 4), "cols_ctas_per_sm" (default 4) and
  * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default),
@@ -318,9 +322,10 @@ int fdl_reduce_cols_f32(const float* x, int64_t batch, int64_t rows, int64_t col
  * dl::kernels::softmax for every SoftmaxAlgo value (include/dl/kernels/softmax.hpp:15-16,
  * src/kernels/cuda/softmax.cu:28-254,272-285).
  * Both row-wise normalisations read a row once and write it once up to 131072 floats per row
- * (registers of one CTA up to 16384, of a thread-block cluster of 2, 4 or 8 CTAs beyond);
- * longer rows take two kernels (per-segment statistics combined per row through the library's
- * workspace, then applied: two reads, one write). */
+ * (registers of one CTA up to 16384 floats; beyond, the registers -- or, for row lengths that
+ * are not a multiple of 4 floats or bases off the 16-byte grid, the shared memory -- of a
+ * thread-block cluster of 2, 4 or 8 CTAs); longer rows take two kernels (per-segment statistics
+ * combined per row through the library's workspace, then applied: two reads, one write). */
 int fdl_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols,
                          void* stream);
 

@@ -15,8 +15,9 @@ SHAPES = [(1, 1), (2, 4), (3, 5), (7, 128), (100, 132), (33, 1000), (64, 1024), 
           # lengths that are not a multiple of 4 floats: 128-bit accesses over the flat buffer, masked edges
           (7, 127), (1000, 63), (50000, 7), (513, 255), (65, 1001), (33, 1023), (19, 4095), (11, 8191), (5, 16381),
           (4, 16383), (1000, 2), (999, 3), (300, 129), (17, 2049),
-          # longer still: segments + per-row combination (two kernels)
-          (3, 262144), (5, 200004), (2, 1 << 20), (1, 3000000), (2, 131077)]
+          # longer still: the row in a cluster's shared memory (8 or 16 CTAs), then segments + per-row combination
+          (3, 262144), (5, 200004), (2, 1 << 20), (1, 3000000), (2, 131077), (40, 50257), (3, 300000), (3, 300001),
+          (2, 500004), (2, 524288), (3, 800003), (2, 900000)]
 
 
 def dev(cuda, a):
@@ -162,8 +163,37 @@ def test_direct_and_staged_forms_agree(fdl, cuda, rows, cols):
         assert np.array_equal(out[-1][k].view(np.uint32), out[picked][k].view(np.uint32))
 
 
+@pytest.mark.parametrize("rows,cols", [(6, 16390), (3, 50257), (5, 65540), (4, 131072), (3, 262144), (2, 400002), (2, 524288)])
+def test_shared_memory_cluster_form_agrees_with_the_other_forms(fdl, cuda, rows, cols):
+    """Long rows kept in a cluster's shared memory (the default) against the register-cluster and
+    two-kernel forms (tuning key rows_smem = 0) and against the fp64 oracle, with statistics."""
+    rng = np.random.default_rng(cols)
+    x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+    g = rng.uniform(0.9, 1.1, cols).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, cols).astype(np.float32)
+    xd, gd, bd = dev(cuda, x), dev(cuda, g), dev(cuda, b)
+    out = {}
+    for mode in (1, 0):
+        fdl.set_tuning("rows_smem", mode)
+        try:
+            sm = to_np(fdl.softmax_rows(xd))
+            ln, mean, rstd = (to_np(t) for t in fdl.layernorm_rows(xd, gd, bd, want_stats=True))
+        finally:
+            fdl.set_tuning("rows_smem", 1)
+        out[mode] = (sm, ln, mean, rstd)
+    fdl.take_device_error()
+    assert_close_scaled(out[1][0], orc.softmax_rows_f64(x), "softmax vs fp64")
+    assert_close_scaled(out[1][1], orc.layernorm_rows_f64(x, g, b, 1e-5), "layernorm vs fp64")
+    assert np.abs(out[1][0].sum(axis=1) - 1).max() <= 1e-5
+    x64 = x.astype(np.float64)
+    assert np.abs(out[1][2] - x64.mean(axis=1)).max() <= 1e-5
+    assert np.abs(out[1][3] / (1 / np.sqrt(x64.var(axis=1) + 1e-5)) - 1).max() <= 1e-5
+    assert_close_scaled(out[1][0], out[0][0], "softmax: shared-memory form vs the other forms")
+    assert_close_scaled(out[1][1], out[0][1], "layernorm: shared-memory form vs the other forms")
+
+
 @pytest.mark.parametrize("rows,cols", [(64, 1024), (100, 1001), (1000, 63), (7, 4096), (9, 8190), (5, 16380),
-                                       (3, 40001), (2, 20000), (2, 140002)])
+                                       (3, 40001), (2, 20000), (2, 140002), (3, 65537), (2, 460001)])
 @pytest.mark.parametrize("x_off,y_off", [(1, 1), (3, 3), (2, 2), (1, 2), (0, 1)])
 def test_rows_at_any_phase_of_a_16_byte_line(fdl, cuda, rows, cols, x_off, y_off):
     """Views whose base is not 16-byte aligned: same phase for x and y (the masked form) and
