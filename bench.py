@@ -14,10 +14,17 @@ per GPU -- far more than the L2; in the end-to-end leg x and y are host tensors.
     python bench.py [--gpus N] [--steps K] [--warmup W]          # this repository's CUDA path
     python bench.py --impl reference [...]                       # the reference's CPU code on the host cores
 
-Prints ONE JSON line (rank 0).  `value`: whole-job algorithmic GB/s, inputs resident in HBM.
-`e2e`: the same metric through the host-buffer C-ABI entry point (pinned host tensors in,
-results in host memory, copies inside the timed region).  `roofline`: the dominant kernel
-(the binary add).  `cpu_baseline`: the reference's CPU code on this box's host cores.
+Prints ONE JSON line (rank 0).  `value`: whole-job algorithmic GB/s, inputs resident in HBM,
+K steps launched back to back.  `per_op` / `roofline`: a second pass with an event between
+the launches (the dominant kernel is the binary add).  `sustained`: the same step repeated for
+at least a second with the clocks sampled.  `check`: the results of one more step verified on
+every rank -- z and w bit for bit against torch, the sums against an fp64 sum (an NCCL
+all-reduce of the ranks' fp64 sums at N > 1), all ranks' result bits against each other; a
+mismatch makes the run exit non-zero.  `config4_per_op`: row softmax / layernorm on
+[65536,1024] sharded by rows over the N ranks.  `e2e`: the same metric through the host-buffer
+C-ABI entry point (pinned host tensors in, results in host memory, copies inside the timed
+region), beside the three separate host calls.  `cpu_baseline`: the reference's CPU code on
+this box's host cores.
 """
 from __future__ import annotations
 
