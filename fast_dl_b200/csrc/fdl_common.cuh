@@ -45,7 +45,8 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 struct Tuning {
     int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
     int cols_tx = 64;            // column reduction: threads across columns per CTA (16..256)
-    int cols_cluster = 4;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8)
+    int cols_cluster = 0;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8, 16; 0 = 8 on the
+                                 // 128-bit path, 2 on the 32-bit path)
     int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
     int cols_chunks = 0;         // column reduction: row chunks per column block (0 = derived)
     int cols_single = 1;         // column reduction: prefer one cluster of 8 per column block where it fits

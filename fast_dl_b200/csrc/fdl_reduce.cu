@@ -1334,10 +1334,19 @@ int cols_geometry(int sm_count, int64_t batch, int64_t rows, int64_t cols, bool 
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks < 1) chunks = 1;
     if (chunks > 65535) chunks = 65535;
-    g->rows_per_chunk = static_cast<int>(ceil_div(rows, chunks));
+    int64_t per_chunk = ceil_div(rows, chunks);
+    // Whole batches of eight rows per thread row: the rows left over after the last full batch
+    // are loaded one per trip, a memory latency each, at the end of EVERY chunk.  Rounding the
+    // chunk up to a multiple of the batch leaves such a tail in the last chunk only.
+    const int64_t batch_rows = static_cast<int64_t>(ty) * 8;
+    if (per_chunk >= 4 * batch_rows) per_chunk = ceil_div(per_chunk, batch_rows) * batch_rows;
+    g->rows_per_chunk = static_cast<int>(per_chunk);
     g->chunks = static_cast<int>(ceil_div(rows, g->rows_per_chunk));
     g->cluster = 1;
-    const int want_cluster = tuning().cols_cluster;
+    // Chunk CTAs per cluster: eight on the 128-bit path (half as many partials and tickets as four:
+    // [2097152,32] 49.2 -> 47.1 us), two on the 32-bit path of odd column counts ([65536,1001]
+    // 58 -> 53 us), unless the tuning key says otherwise.
+    const int want_cluster = tuning().cols_cluster > 0 ? tuning().cols_cluster : (vec ? 8 : 2);
     if (want_cluster > 1 && g->chunks >= want_cluster) {
         // Round up to whole clusters; trailing chunks may be empty (they contribute the
         // identity).

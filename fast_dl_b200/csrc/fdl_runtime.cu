@@ -167,7 +167,7 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().cols_tx = value;
         return FDL_OK;
     }
-    if (k == "cols_cluster" && (value == 1 || value == 2 || value == 4 || value == 8 || value == 16)) {
+    if (k == "cols_cluster" && (value == 0 || value == 1 || value == 2 || value == 4 || value == 8 || value == 16)) {
         fdl::tuning().cols_cluster = value;
         return FDL_OK;
     }

@@ -114,7 +114,8 @@ int fdl_take_device_error(void);
  * "rows_smem_cluster" (CTAs per row in that form: 2, 4, 8, 16, or 0 = by row length; default 0),
  * "rows_smem_from" (aligned rows longer than this many floats take that form; 0 = 65536, default),
  * and for the column reductions "cols_tx" (threads across columns per CTA: 16..256; default
- * 64), "cols_cluster" (1, 2, 4, 8, 16; default 4), "cols_ctas_per_sm" (default 4) and
+ * 64), "cols_cluster" (1, 2, 4, 8, 16, or 0 = 8 with 128-bit loads and 2 with 32-bit loads; default
+ * 0), "cols_ctas_per_sm" (default 4) and
  * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default),
  * "cols_single" (1 = where the shape allows, one cluster of 8 CTAs covers all rows of a column
  * block and nothing goes through scratch; 0 = always the chunked form; default 1);
