@@ -55,6 +55,10 @@ struct Tuning {
                                  // lane (1), by a 256-thread CTA (0), or whichever measured faster (-1)
     int rows_staged = -1;  // row softmax/layernorm: 0 = direct loads, 1 = one bulk-async copy per CTA,
                            // -1 = staged for rows of up to 128 floats, direct beyond
+    int rows_span_reduce_cols = 2048;  // row reductions: rows of up to this many floats at an odd length or
+                                       // phase are staged as runs of rows through shared memory (0 = never)
+    int rows_span_cols = 256;  // row softmax/layernorm: rows of up to this many floats at an odd length or phase
+                               // are staged as runs of rows through shared memory (0 = never; at most 256)
     int rows_smem = 1;     // row softmax/layernorm: long rows in a cluster's shared memory, read once (0 = the
                            // register-cluster and two-kernel forms)
     int rows_smem_from = 0;     // aligned rows longer than this many floats take that form (0 = 65536)

@@ -941,6 +941,105 @@ int launch_rows_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out*
                      dim3(1, 1, 1), tuning().pdl != 0, x, rows, static_cast<int>(cols), out, static_cast<float>(cols), phase);
 }
 
+// ---- span form: rows at any phase of a 16-byte line, staged through shared memory -------------------
+//
+// Row lengths that are not a multiple of 4 floats (or a base off the 16-byte grid), up to 2048
+// floats.  Consecutive rows are one contiguous run of memory whatever their length: a CTA takes
+// a run of rows, thread 0 asks the copy engine for the aligned packs that cover it (one bulk-async
+// copy, ~40 KiB in flight per CTA without a register held), and teams of lanes reduce their rows
+// out of shared memory float by float -- consecutive lanes, consecutive floats, four independent
+// chains a lane.  (The flat-pack forms above give such rows 40-65% of the copy bandwidth: one row
+// per warp at a time, two dependent edge loads.)
+constexpr int kRowSpanBytes = 40 * 1024;
+constexpr int kRowSpanMaxCols = 2048;
+
+template <class R, int TPR>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_rows_span_kernel(const float* x, int64_t rows, int cols, typename R::Out* out, float divisor, int phase,
+                        int rows_per_cta, unsigned int* error_flag) {
+    using State = typename R::State;
+    constexpr int kTeams = kRowThreads / TPR;
+    extern __shared__ __align__(128) unsigned char span_raw[];
+    const float* buf = reinterpret_cast<const float*>(span_raw);
+    __shared__ uint64_t bar;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+    const int64_t left = rows - r0;
+    const int nr = static_cast<int>(left < rows_per_cta ? left : rows_per_cta);
+    const int64_t e_lo = phase + r0 * cols;  // first float of the run, counted from the 16-byte line of x[0]
+    const int64_t e_hi = e_lo + static_cast<int64_t>(nr) * cols;
+    const int64_t pk_lo = e_lo >> 2;
+    const int npk = static_cast<int>(((e_hi + 3) >> 2) - pk_lo);
+    const int base = static_cast<int>(e_lo - 4 * pk_lo);
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_wait();  // the input may be the previous kernel's output
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(&bar, static_cast<uint32_t>(npk) * 16u);
+        bulk_g2s(span_raw, reinterpret_cast<const float4*>(x - phase) + pk_lo, static_cast<uint32_t>(npk) * 16u, &bar);
+    }
+    bool landed = mbar_wait_bounded(&bar, 0);
+    landed = __syncthreads_and(landed);
+    pdl_trigger();
+    if (!landed) {
+        if (threadIdx.x == 0) atomicOr(error_flag, 1u);
+        return;
+    }
+    // Team k takes rows k, k + kTeams, ...; the same number of trips for every team, so that the
+    // sub-warp teams of a warp shuffle together.
+    const int trips = (nr + kTeams - 1) / kTeams;
+    for (int trip = 0; trip < trips; ++trip) {
+        const int i = trip * kTeams + team;
+        const bool active = i < nr;
+        const float* rowp = buf + base + (active ? i : 0) * cols;
+        State acc[kRowUnroll];
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
+        if (active) {
+            for (int c = t; c < cols; c += TPR * kRowUnroll) {
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) {
+                    const int cc = c + u * TPR;
+                    if (cc < cols) acc[u] = R::combine(acc[u], R::lift(rowp[cc], cc));
+                }
+            }
+        }
+        State s = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
+        if (active && t == 0) out[r0 + i] = R::finish(s, cols, divisor);
+    }
+}
+
+template <class R, int TPR>
+int launch_rows_span_cfg(const float* x, int64_t rows, int64_t cols, typename R::Out* out, cudaStream_t stream) {
+    static_assert(kRowUnroll == 4, "four chains are combined pairwise above");
+    unsigned int* flag = nullptr;
+    const int st = error_flag_device_ptr(&flag);
+    if (st != FDL_OK) return st;
+    int64_t rows_per_cta = (kRowSpanBytes - 32) / (cols * 4);
+    if (rows_per_cta < 1) return FDL_ERR_UNSUPPORTED;
+    if (rows_per_cta > rows) rows_per_cta = rows;
+    const int64_t grid = ceil_div(rows, rows_per_cta);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    const size_t smem = static_cast<size_t>((rows_per_cta * cols + 6) / 4 + 1) * 16;
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(x) & 15u) / 4u);
+    return launch_ex(reduce_rows_span_kernel<R, TPR>, dim3(static_cast<unsigned int>(grid)), dim3(kRowThreads), smem,
+                     stream, dim3(1, 1, 1), tuning().pdl != 0, x, rows, static_cast<int>(cols), out,
+                     static_cast<float>(cols), phase, static_cast<int>(rows_per_cta), flag);
+}
+
+template <class R>
+int launch_rows_span(const float* x, int64_t rows, int64_t cols, typename R::Out* out, cudaStream_t stream) {
+    if (cols <= 32) return launch_rows_span_cfg<R, 8>(x, rows, cols, out, stream);
+    if (cols <= 128) return launch_rows_span_cfg<R, 16>(x, rows, cols, out, stream);
+    return launch_rows_span_cfg<R, 32>(x, rows, cols, out, stream);
+}
+
 template <class R>
 int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out,
                 cudaStream_t stream) {
@@ -949,6 +1048,12 @@ int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out
     if (x == nullptr || out == nullptr || cols == 0) return FDL_ERR_INVALID_ARGUMENT;
     if (cols >= INT_MAX - 16) return FDL_ERR_UNSUPPORTED;  // pack arithmetic on a row stays inside int
     const bool vec = aligned16(x) && cols % 4 == 0;
+    // (argmax on rows of up to 64 floats stays with the team kernels: its (value, index) pairs
+    // cost two shuffles a step and the span form measured 50% against 60% on [1048576,63])
+    if (!vec && cols <= tuning().rows_span_reduce_cols && cols <= kRowSpanMaxCols && !(R::kIsArgmax && cols <= 64)) {
+        const int st = launch_rows_span<R>(x, rows, cols, out, stream);
+        if (st != FDL_ERR_UNSUPPORTED) return st;
+    }
     if ((vec ? cols / 4 : cols) <= kNarrowMaxItems) {
         return vec ? launch_rows_narrow<R, 4>(x, rows, cols, out, stream)
                    : launch_rows_narrow<R, 1>(x, rows, cols, out, stream);

@@ -212,7 +212,7 @@ __device__ __forceinline__ void row_math(LayerNormOp, float4 (&v)[NV], int t, in
 // Registers per thread are capped so that several CTAs stay resident per SM: the bytes in
 // flight per SM are (resident CTAs) x (bytes a CTA requests), and the arithmetic is light.
 constexpr int min_ctas_for(int th, int nv) {
-    return th > 256 ? (nv <= 4 ? 3 : 2) : (nv <= 4 ? 6 : (nv <= 8 ? 4 : 2));
+    return th > 256 ? (nv <= 4 ? 3 : 2) : (nv <= 4 ? 6 : (nv <= 9 ? 4 : 2));
 }
 
 // ---- direct form ----------------------------------------------------------------------------------
@@ -508,6 +508,163 @@ int launch_masked_short_cfg(const RowParams& p, cudaStream_t stream) {
     const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
     rows_masked_short_kernel<Op, TPR, U><<<static_cast<unsigned int>(grid), 256, 0, stream>>>(p, phase);
     return launch_status();
+}
+
+// ---- span form: short rows at any phase, staged through shared memory -----------------------------
+//
+// Rows of up to a few hundred floats whose length is not a multiple of 4 (or whose base is off
+// the 16-byte grid).  In the masked form above a lane of such a row has a single 128-bit load
+// in flight and the edge packs go float by float ([1048576,63]: 41-52% of the copy bandwidth).
+// But consecutive rows are one contiguous run of memory whatever the row length: a CTA takes
+// a run of rows, thread 0 asks the copy engine for the aligned packs that cover the run (one
+// bulk-async copy, ~40 KiB in flight per CTA without a register held), teams of lanes then
+// walk their rows float by float in shared memory -- consecutive lanes, consecutive floats --
+// and write the results back in place, and the whole CTA stores the run as 128-bit packs.  Only
+// the first and the last pack of the run can be shared with a neighbouring CTA's rows; those
+// two are stored one valid float at a time.  x and y must sit at the same phase.
+template <class Op, int TPR, int NVS>
+__global__ void __launch_bounds__(256)
+rows_span_kernel(const RowParams p, int phase, int rows_per_cta) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr int kTeams = 256 / TPR;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* buf = reinterpret_cast<float*>(smem_raw);
+    __shared__ uint64_t bar;
+    const int team = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+    int64_t nr64 = p.rows - r0;
+    const int nr = static_cast<int>(nr64 < rows_per_cta ? nr64 : rows_per_cta);
+    const int64_t e_lo = phase + r0 * p.cols;                     // first float of the run, from the line of x[0]
+    const int64_t e_hi = e_lo + static_cast<int64_t>(nr) * p.cols;
+    const int64_t pk_lo = e_lo >> 2;
+    const int npk = static_cast<int>(((e_hi + 3) >> 2) - pk_lo);
+    const int base = static_cast<int>(e_lo - 4 * pk_lo);          // where the run starts inside the first pack
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_wait();  // the input may be the previous kernel's output
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(&bar, static_cast<uint32_t>(npk) * 16u);
+        bulk_g2s(buf, reinterpret_cast<const float4*>(p.x - phase) + pk_lo, static_cast<uint32_t>(npk) * 16u, &bar);
+    }
+    bool landed = mbar_wait_bounded(&bar, 0);
+    landed = __syncthreads_and(landed);
+    pdl_trigger();
+    if (!landed) {
+        if (threadIdx.x == 0) atomicOr(p.error_flag, 1u);
+        return;
+    }
+    const float neutral = kSoftmax ? -INFINITY : 0.0f;
+    const float inv_n = 1.0f / static_cast<float>(p.cols);
+    // Team k takes rows k, k + kTeams, ...; every team runs the same number of trips, so that
+    // the sub-warp teams of a warp shuffle together.
+    const int trips = (nr + kTeams - 1) / kTeams;
+    for (int trip = 0; trip < trips; ++trip) {
+        const int i = trip * kTeams + team;
+        const bool active = i < nr;
+        float* rowp = buf + base + (active ? i : 0) * p.cols;
+        float v[NVS];
+#pragma unroll
+        for (int k = 0; k < NVS; ++k) {
+            const int c = t + k * TPR;
+            v[k] = active && c < p.cols ? rowp[c] : neutral;
+        }
+        float a = v[0];
+#pragma unroll
+        for (int k = 1; k < NVS; ++k) a = kSoftmax ? fmaxf(a, v[k]) : a + v[k];
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(kFullMask, a, o);
+            a = kSoftmax ? fmaxf(a, other) : a + other;
+        }
+        if (!kSoftmax) a *= inv_n;
+        float b = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NVS; ++k) {
+            const int c = t + k * TPR;
+            if (kSoftmax) {
+                v[k] = fast_exp2((v[k] - a) * kLog2e);  // exp2(-inf) = 0 for the lanes beyond the row
+                b += v[k];
+            } else {
+                const float d = active && c < p.cols ? v[k] - a : 0.0f;
+                b += d * d;
+            }
+        }
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) b += __shfl_xor_sync(kFullMask, b, o);
+        if (!active) continue;
+        // Rows this short pay for every instruction per row: the reciprocal square root is the
+        // hardware's approximate one (2 ulp), where the longer-row forms divide by sqrtf.
+        const float scale = kSoftmax ? 1.0f / b : rsqrtf(b * inv_n + p.eps);
+        if (!kSoftmax && t == 0) {
+            if (p.mean_out != nullptr) p.mean_out[r0 + i] = a;
+            if (p.rstd_out != nullptr) p.rstd_out[r0 + i] = scale;
+        }
+#pragma unroll
+        for (int k = 0; k < NVS; ++k) {
+            const int c = t + k * TPR;
+            if (c < p.cols) {
+                float o = kSoftmax ? v[k] * scale : (v[k] - a) * scale;
+                if (!kSoftmax) {
+                    if (p.gamma != nullptr) o *= __ldg(p.gamma + c);
+                    if (p.beta != nullptr) o += __ldg(p.beta + c);
+                }
+                rowp[c] = o;
+            }
+        }
+    }
+    __syncthreads();
+    // The run goes out as aligned packs; only its first and last pack can hold foreign floats.
+    float4* dst = reinterpret_cast<float4*>(p.y - phase) + pk_lo;
+    const float4* out4 = reinterpret_cast<const float4*>(buf);
+    const int tail = static_cast<int>(e_hi & 3);
+    for (int i = threadIdx.x; i < npk; i += 256) {
+        const bool first = i == 0 && base != 0;
+        const bool last = i == npk - 1 && tail != 0;
+        if (!first && !last) {
+            st_stream(dst + i, out4[i]);
+        } else {
+            float* q = reinterpret_cast<float*>(dst + i);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int64_t e = 4 * (pk_lo + i) + k;
+                if (e >= e_lo && e < e_hi) q[k] = buf[4 * i + k];
+            }
+        }
+    }
+}
+
+constexpr int kSpanBytes = 40 * 1024;  // of shared memory per CTA: five CTAs per SM
+
+template <class Op, int TPR, int NVS>
+int launch_span_cfg(const RowParams& p, cudaStream_t stream) {
+    const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
+    int64_t rows_per_cta = (kSpanBytes - 32) / (static_cast<int64_t>(p.cols) * 4);
+    if (rows_per_cta < 1) return FDL_ERR_UNSUPPORTED;
+    if (rows_per_cta > p.rows) rows_per_cta = p.rows;
+    const int64_t grid = ceil_div(p.rows, rows_per_cta);
+    if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
+    const size_t smem = static_cast<size_t>((rows_per_cta * p.cols + 6) / 4 + 1) * 16;
+    return launch_ex(rows_span_kernel<Op, TPR, NVS>, dim3(static_cast<unsigned int>(grid)), dim3(256), smem, stream,
+                     dim3(1, 1, 1), tuning().pdl != 0, p, phase, static_cast<int>(rows_per_cta));
+}
+
+// Team size and values per lane for a row of `cols` floats (at most 256).
+template <class Op>
+int launch_span(const RowParams& p, cudaStream_t stream) {
+    const int c = p.cols;
+    if (c <= 8) return launch_span_cfg<Op, 8, 1>(p, stream);
+    if (c <= 16) return launch_span_cfg<Op, 8, 2>(p, stream);
+    if (c <= 32) return launch_span_cfg<Op, 8, 4>(p, stream);
+    if (c <= 64) return launch_span_cfg<Op, 16, 4>(p, stream);
+    if (c <= 128) return launch_span_cfg<Op, 32, 4>(p, stream);
+    if (c <= 256) return launch_span_cfg<Op, 32, 8>(p, stream);
+    return FDL_ERR_UNSUPPORTED;
 }
 
 template <class Op, int TPR, int TH, int NV>
@@ -1340,7 +1497,10 @@ bool warp_takes_16_packs(int nvec) {
     return std::is_same<Op, LayerNormOp>::value || nvec <= 320;
 }
 
-// Picks the team size and the registers-per-thread bucket for a row length.
+// Picks the team size and the registers-per-thread bucket for a row length.  The buckets of nine
+// packs a thread sit just above the powers of two: a row of 1023 or 8191 floats at an odd phase
+// covers 257 or 2049 packs, one more than the eight-pack bucket holds, and would otherwise
+// land in a bucket of twice the registers (76-82% and 73-76% of the copy bandwidth).
 #define FDL_ROW_DISPATCH(LAUNCH) FDL_ROW_DISPATCH_N(LAUNCH, p.cols / 4)
 #define FDL_ROW_DISPATCH_N(LAUNCH, NVEC)                                                 \
     do {                                                                                 \
@@ -1351,10 +1511,12 @@ bool warp_takes_16_packs(int nvec) {
         if (nvec_ <= 64) return LAUNCH<Op, 32, 256, 2>(p, info, stream);                 \
         if (nvec_ <= 128) return LAUNCH<Op, 32, 256, 4>(p, info, stream);                \
         if (nvec_ <= 256) return LAUNCH<Op, 32, 256, 8>(p, info, stream);                \
+        if (nvec_ <= 288) return LAUNCH<Op, 32, 256, 9>(p, info, stream);                \
         if (nvec_ <= 512 && warp_takes_16_packs<Op>(nvec_)) return LAUNCH<Op, 32, 256, 16>(p, info, stream); \
         if (nvec_ <= 512) return LAUNCH<Op, 256, 256, 2>(p, info, stream);               \
         if (nvec_ <= 1024) return LAUNCH<Op, 256, 256, 4>(p, info, stream);              \
         if (nvec_ <= 2048) return LAUNCH<Op, 256, 256, 8>(p, info, stream);              \
+        if (nvec_ <= 2304) return LAUNCH<Op, 256, 256, 9>(p, info, stream);              \
         return LAUNCH<Op, 512, 512, 8>(p, info, stream);                                 \
     } while (0)
 
@@ -1408,6 +1570,10 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     const int64_t packs_worst = (static_cast<int64_t>(p.cols) + 6) / 4;
     if (!packs && ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0 &&
         packs_worst <= kCtaMaxCols / 4) {
+        if (p.cols <= tuning().rows_span_cols) {
+            const int st = launch_span<Op>(p, stream);
+            if (st != FDL_ERR_UNSUPPORTED) return st;
+        }
         if (packs_worst <= 8) return launch_masked_short_cfg<Op, 8>(p, stream);
         if (packs_worst <= 16) return launch_masked_short_cfg<Op, 16>(p, stream);
         if (packs_worst <= 32) return launch_masked_short_cfg<Op, 32>(p, stream);

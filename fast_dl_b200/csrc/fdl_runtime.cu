@@ -199,6 +199,14 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().rows_smem_cluster = value;
         return FDL_OK;
     }
+    if (k == "rows_span_reduce_cols" && value >= 0 && value <= 2048) {
+        fdl::tuning().rows_span_reduce_cols = value;
+        return FDL_OK;
+    }
+    if (k == "rows_span_cols" && value >= 0 && value <= 256) {
+        fdl::tuning().rows_span_cols = value;
+        return FDL_OK;
+    }
     if (k == "rows_smem_from" && value >= 0) {
         fdl::tuning().rows_smem_from = value;
         return FDL_OK;
