@@ -10,10 +10,15 @@
 // Which kernel a row reduction takes depends on the shape: rows of up to 256 floats go to
 // teams of lanes with several rows in flight, longer ones to a warp or a CTA per row, a few
 // very long rows are cut into segments (one CTA each, folded per row through scratch), and
-// rows at an arbitrary phase of a 16-byte line (odd lengths, unaligned bases) are walked
-// as aligned packs of the flat buffer with their two edge packs read float by float.
+// rows at an arbitrary phase of a 16-byte line (odd lengths, unaligned bases) are staged as
+// runs of consecutive rows through shared memory by one bulk-async copy per CTA (up to 2048
+// floats a row) or walked as aligned packs of the flat buffer with their two edge packs read
+// float by float (beyond).
 // Column reductions have a tree-free form for up to 8 rows and own four columns per thread
-// (adjacent with 128-bit loads, a tile-width apart with 32-bit loads).
+// (adjacent with 128-bit loads, a tile-width apart with 32-bit loads); where the shape allows,
+// one cluster of eight CTAs covers all the rows of a column block and nothing goes through
+// scratch.  The streaming kernels are launched with programmatic stream serialization and wait
+// for the previous kernel of the stream before their first global access.
 #include <cooperative_groups.h>
 
 #include <cfloat>

@@ -26,13 +26,23 @@
 // through distributed shared memory, so such a row is still read once and written once.
 // Longer rows are cut into 32 KiB segments: one kernel leaves per-segment statistics and
 // combines them per row, a second applies them (two reads, one write).
-// Rows whose length is not a multiple of 4 floats, or whose base is not 16-byte aligned, take
-// the masked form (128-bit accesses laid over the flat buffer, edge packs lane by lane) up to
-// 16384 floats; what is left (such rows beyond that, x and y at different phases) takes a plain
-// three-pass kernel (second and third pass hit L2 while a row fits there).
+// Rows whose length is not a multiple of 4 floats, or whose base is not 16-byte aligned (x and y
+// at the same phase), are read once too:
+//   up to 256 floats    the span form: a CTA takes a run of consecutive rows -- one contiguous run of
+//                       memory whatever the row length --, one bulk-async copy brings in the aligned
+//                       packs that cover it, teams walk their rows float by float in shared memory;
+//   up to 16384 floats  the masked form: 128-bit accesses laid over the flat buffer, the row in
+//                       registers, edge packs lane by lane (buckets of nine packs a thread just above
+//                       the powers of two, where a row at an odd phase covers one pack more);
+//   up to 131072 floats the shared-memory cluster form: a cluster of 2, 4 or 8 CTAs keeps the row in
+//                       shared memory (slices of up to 64 KiB, bulk-async copies), one exchange of
+//                       slice statistics through distributed shared memory.
+// What is left (longer such rows: the two-kernel form; x and y at different phases: a plain
+// three-pass kernel whose second and third pass hit L2 while a row fits there).
 //
-// The one mbarrier wait is bounded; if it runs out the CTA raises a flag in host-visible
-// memory (fdl_take_device_error) and leaves without touching the output.
+// Every mbarrier wait is bounded; if one runs out the CTA raises a flag in host-visible
+// memory (fdl_take_device_error) and stores nothing (in a cluster it still walks through the
+// cluster barriers, where its peers wait).
 #include <climits>
 #include <cmath>
 #include <type_traits>
