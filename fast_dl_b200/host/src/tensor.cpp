@@ -139,39 +139,56 @@ void* TensorImpl::data() { return block_ ? block_->ptr : nullptr; }
 const void* TensorImpl::data() const { return block_ ? block_->ptr : nullptr; }
 std::size_t TensorImpl::nbytes() const { return static_cast<std::size_t>(numel()) * dtype_size(dtype_); }
 
+namespace {
+// One blocking cudaMemcpy / cudaMemset on `device`, with the library's error convention.  The four
+// data-moving members below differ only in their size rule, their direction and their messages.
+struct DeviceOp {
+    int device;
+    explicit DeviceOp(const Device& d, const char* cuda_only_message) : device(d.index) {
+        if (!d.is_cuda()) throw std::runtime_error(cuda_only_message);
+        dl::cuda::check(cudaSetDevice(device), "cudaSetDevice failed");
+    }
+    void copy(void* dst, const void* src, std::size_t bytes, cudaMemcpyKind kind, const char* failure) const {
+        dl::cuda::check(cudaMemcpy(dst, src, bytes, kind), failure);
+    }
+};
+
+void require_fits(std::size_t bytes, std::size_t capacity, const char* message) {
+    if (bytes > capacity) throw std::runtime_error(message);
+}
+}  // namespace
+
 void TensorImpl::copy_from_host(const void* src, std::size_t bytes) {
-    if (bytes > nbytes()) throw std::runtime_error("copy_from_host exceeds tensor size");
-    if (bytes == 0) return;
-    if (!device_.is_cuda()) throw std::runtime_error("copy_from_host currently supports CUDA tensors only");
-    dl::cuda::check(cudaSetDevice(device_.index), "cudaSetDevice failed");
-    dl::cuda::check(cudaMemcpy(data(), src, bytes, cudaMemcpyHostToDevice), "cudaMemcpy host to device failed");
+    require_fits(bytes, nbytes(), "copy_from_host exceeds tensor size");
+    if (bytes != 0) {
+        DeviceOp(device_, "copy_from_host currently supports CUDA tensors only")
+            .copy(data(), src, bytes, cudaMemcpyHostToDevice, "cudaMemcpy host to device failed");
+    }
 }
 
 void TensorImpl::copy_to_host(void* dst, std::size_t bytes) const {
-    if (bytes > nbytes()) throw std::runtime_error("copy_to_host exceeds tensor size");
-    if (bytes == 0) return;
-    if (!device_.is_cuda()) throw std::runtime_error("copy_to_host currently supports CUDA tensors only");
-    dl::cuda::check(cudaSetDevice(device_.index), "cudaSetDevice failed");
-    dl::cuda::check(cudaMemcpy(dst, data(), bytes, cudaMemcpyDeviceToHost), "cudaMemcpy device to host failed");
+    require_fits(bytes, nbytes(), "copy_to_host exceeds tensor size");
+    if (bytes != 0) {
+        DeviceOp(device_, "copy_to_host currently supports CUDA tensors only")
+            .copy(dst, data(), bytes, cudaMemcpyDeviceToHost, "cudaMemcpy device to host failed");
+    }
 }
 
 void TensorImpl::copy_from(const TensorImpl& src) {
-    if (src.nbytes() != nbytes()) throw std::runtime_error("tensor copy size mismatch");
-    if (nbytes() == 0) return;
-    if (!(src.device().is_cuda() && device_.is_cuda())) {
-        throw std::runtime_error("copy_from currently supports CUDA to CUDA only");
-    }
-    dl::cuda::check(cudaSetDevice(device_.index), "cudaSetDevice failed");
+    const std::size_t bytes = nbytes();
+    if (src.nbytes() != bytes) throw std::runtime_error("tensor copy size mismatch");
+    if (bytes == 0) return;
+    const char* cuda_only = "copy_from currently supports CUDA to CUDA only";
+    if (!src.device().is_cuda()) throw std::runtime_error(cuda_only);
     // cudaMemcpyDefault also covers a source on another GPU (peer copy through the driver).
-    dl::cuda::check(cudaMemcpy(data(), src.data(), nbytes(), cudaMemcpyDefault),
-                    "cudaMemcpy device to device failed");
+    DeviceOp(device_, cuda_only).copy(data(), src.data(), bytes, cudaMemcpyDefault, "cudaMemcpy device to device failed");
 }
 
 void TensorImpl::zero_() {
-    if (nbytes() == 0) return;
-    if (!device_.is_cuda()) throw std::runtime_error("zero_ currently supports CUDA tensors only");
-    dl::cuda::check(cudaSetDevice(device_.index), "cudaSetDevice failed");
-    dl::cuda::check(cudaMemset(data(), 0, nbytes()), "cudaMemset failed");
+    const std::size_t bytes = nbytes();
+    if (bytes == 0) return;
+    const DeviceOp op(device_, "zero_ currently supports CUDA tensors only");
+    dl::cuda::check(cudaMemset(data(), 0, bytes), "cudaMemset failed");
 }
 
 // ---- Tensor ---------------------------------------------------------------------------------------
@@ -224,18 +241,29 @@ Tensor Tensor::uniform(Shape shape, DType dtype, Device device, float low, float
     return random_fill(shape, dtype, device, false, low, high, seed, "Tensor::uniform");
 }
 
+namespace {
+// The two fan sizes of a weight of rank >= 2: its last two extents.
+struct Fans {
+    float in, out;
+    Fans(const Shape& shape, const char* who) {
+        if (shape.rank() < 2) throw std::runtime_error(std::string(who) + " requires rank >= 2");
+        const int r = static_cast<int>(shape.rank());
+        in = static_cast<float>(shape[r - 2]);
+        out = static_cast<float>(shape[r - 1]);
+    }
+};
+}  // namespace
+
+// uniform(-limit, limit) with limit = sqrt(6 / (fan_in + fan_out)) (Xavier) or sqrt(6 / fan_in) (Kaiming).
 Tensor Tensor::xavier_uniform(Shape shape, DType dtype, Device device, uint64_t seed) {
-    if (shape.rank() < 2) throw std::runtime_error("Tensor::xavier_uniform requires rank >= 2");
-    const int r = static_cast<int>(shape.rank());
-    const float fan_in = static_cast<float>(shape[r - 2]), fan_out = static_cast<float>(shape[r - 1]);
-    const float limit = std::sqrt(6.0f / (fan_in + fan_out));
+    const Fans fans(shape, "Tensor::xavier_uniform");
+    const float limit = std::sqrt(6.0f / (fans.in + fans.out));
     return uniform(shape, dtype, device, -limit, limit, seed);
 }
 
 Tensor Tensor::kaiming_uniform(Shape shape, DType dtype, Device device, uint64_t seed) {
-    if (shape.rank() < 2) throw std::runtime_error("Tensor::kaiming_uniform requires rank >= 2");
-    const float fan_in = static_cast<float>(shape[static_cast<int>(shape.rank()) - 2]);
-    const float limit = std::sqrt(6.0f / fan_in);
+    const Fans fans(shape, "Tensor::kaiming_uniform");
+    const float limit = std::sqrt(6.0f / fans.in);
     return uniform(shape, dtype, device, -limit, limit, seed);
 }
 
