@@ -49,6 +49,7 @@ struct Tuning {
                                  // 128-bit path, 2 on the 32-bit path)
     int cols_ctas_per_sm = 4;   // column reduction: CTAs aimed at per SM
     int cols_chunks = 0;         // column reduction: row chunks per column block (0 = derived)
+    int cols_regroup = 1;        // column reduction: odd column counts walked as [rows / 4, 4 * cols] with 128-bit loads
     int cols_single = 1;         // column reduction: prefer one cluster of 8 per column block where it fits
     int rows_cluster_threads = 256;  // cluster form of rows up to 65536 floats: threads per CTA (256 or 512)
     int rows_warp16 = -1;        // row softmax/layernorm: rows of 1028..2048 floats by one warp, 16 packs a

@@ -183,6 +183,10 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().cols_chunks = value;
         return FDL_OK;
     }
+    if (k == "cols_regroup" && (value == 0 || value == 1)) {
+        fdl::tuning().cols_regroup = value;
+        return FDL_OK;
+    }
     if (k == "cols_single" && (value == 0 || value == 1)) {
         fdl::tuning().cols_single = value;
         return FDL_OK;

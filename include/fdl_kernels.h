@@ -122,7 +122,9 @@ int fdl_take_device_error(void);
  * 0), "cols_ctas_per_sm" (default 4) and
  * "cols_chunks" (row chunks per column block; 0 = derived from cols_ctas_per_sm, default),
  * "cols_single" (1 = where the shape allows, one cluster of 8 CTAs covers all rows of a column
- * block and nothing goes through scratch; 0 = always the chunked form; default 1);
+ * block and nothing goes through scratch; 0 = always the chunked form; default 1), "cols_regroup"
+ * (1 = a matrix whose column count is not a multiple of 4 is reduced as [rows / 4, 4 * cols] with
+ * 128-bit loads and its results folded by a second, small kernel; 0 = 32-bit loads; default 1);
  * "pdl" (1 = the streaming kernels are launched with programmatic stream serialization, so
  * that the next kernel's launch overlaps the tail of the one before; 0 = plain launches;
  * default 1), "bcast2d" (1 = two-dimensional broadcasts take the division-free kernel;

@@ -179,11 +179,15 @@ def test_column_reduction_batched_few_rows_and_many_chunks(fdl, cuda):
 
 
 @pytest.mark.parametrize("rows,cols", [(16384, 4), (20000, 8), (1 << 17, 16), (300001, 32), (65536 + 7, 64), (40000, 128),
-                                       (1 << 21, 32)])
+                                       (1 << 21, 32),
+                                       # column counts that are not a multiple of 4: taken 4 (or 2) rows at a time
+                                       # with 128-bit loads, rows left over, results folded by a second kernel
+                                       (300001, 33), (65537, 1001), (70002, 6), (1001, 255), (40, 50257), (9, 7), (13, 2)])
 def test_column_reduction_of_tall_narrow_matrices(fdl, cuda, rows, cols):
     """Rows of 4 ... 128 floats: a single column block, hundreds of row chunks, the last CTA
-    folding them; with the library's and with the caller's scratch, twice in a row (the arrival
-    counters must come back to zero), and the full sum on the same workspace afterwards."""
+    folding them; and odd column counts; with the library's and with the caller's scratch, twice
+    in a row (the arrival counters must come back to zero), and the full sum on the same
+    workspace afterwards."""
     rng = np.random.default_rng(rows + cols)
     x = rng.normal(size=(rows, cols)).astype(np.float32)
     x[rows // 2, cols - 1] = 1e6   # a lone large value must land in its own column
@@ -198,6 +202,13 @@ def test_column_reduction_of_tall_narrow_matrices(fdl, cuda, rows, cols):
         assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX, scratch=use)), x.max(axis=0), "col max")
     assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), "deterministic")
     assert_sum_close(to_np(fdl.full_sum(xd))[0], x64.sum(), np.sqrt((x64 ** 2).sum()), "full sum afterwards")
+    if cols % 4:
+        fdl.set_tuning("cols_regroup", 0)
+        try:
+            assert_sum_close(to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM)), x64.sum(axis=0), norm, "col sum, 32-bit loads")
+            assert_bit_exact(to_np(fdl.reduce_cols(xd, fdl.REDUCE_MAX)), x.max(axis=0), "col max, 32-bit loads")
+        finally:
+            fdl.set_tuning("cols_regroup", 1)
 
 
 @pytest.mark.parametrize("rows,cols", [(8192, 8192), (4096, 8192), (5000, 12288), (2048, 16384), (3000, 32768), (1100, 65536)])
