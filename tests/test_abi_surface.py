@@ -36,6 +36,10 @@ def test_no_gpu_calls_needed_for_metadata(fdl):
     assert b"invalid" in lib.fdl_error_string(-1)
     assert lib.fdl_sum_scratch_bytes(1 << 28) % 256 == 0
     assert lib.fdl_reduce_cols_scratch_bytes(1, 8192, 8192) % 256 == 0
+    # an odd column count is reduced four rows at a time: room for the 4 * cols grouped results
+    odd = lib.fdl_reduce_cols_scratch_bytes(1, 65537, 1001)
+    assert odd % 256 == 0 and odd >= 65536 + 4 * 1001 * 4
+    assert lib.fdl_reduce_cols_scratch_bytes(0, 10, 10) == 0
 
 
 def test_product_does_not_import_the_oracle():
