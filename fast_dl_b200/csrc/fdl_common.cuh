@@ -44,6 +44,11 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // (set through fdl_set_tuning).  Defaults are the measured best on B200.
 struct Tuning {
     int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
+    int rows_split_from = 0;   // > 0: rows of at least this many floats take the split form whatever the other forms offer
+    int rows_split_fused = 1;  // rows beyond a cluster's reach: 1 = one kernel, statistics and apply tasks pipelined through L2; 0 = two kernels
+    int rows_split_lag = 0;    // rows between a row's statistics and its apply tasks in that kernel (0 = 36 MiB of rows)
+    int rows_split_hints = 1;  // L2 eviction-priority hints on that kernel's loads
+    int sum_tiles = 0;     // 32 KiB tiles a CTA of the full sum walks (0 = by size)
     int cols_tx = 64;            // column reduction: threads across columns per CTA (16..256)
     int cols_cluster = 0;        // column reduction: CTAs per cluster along the rows (1, 2, 4, 8, 16; 0 = 8 on the
                                  // 128-bit path, 2 on the 32-bit path)
@@ -201,6 +206,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "r"(smem_addr(bar)), "r"(parity)
         : "memory");
     return done != 0;
+}
+
+__device__ __forceinline__ unsigned long long timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 // Bounded wait: gives up after kMbarSpinLimit polls so a lost copy can never hang the

@@ -460,7 +460,11 @@ int launch_sum(const float* x, int64_t n, float* out_f32, double* out_f64, unsig
     const int64_t nvec = VEC ? n / 4 : 0;
     int64_t tiles = VEC ? ceil_div(nvec, kSumTile) : ceil_div(n, static_cast<int64_t>(kSumTile) * 4);
     if (tiles < 1) tiles = 1;
-    int64_t grid = ceil_div(tiles, CL) * CL;
+    // Tiles a CTA walks (grid-stride).  From 8192 tiles (256 MiB) on, two per CTA halve the number
+    // of cluster exchanges and tickets: measured 45.8 -> 45.1 us at 256 MiB, 153.6 -> 151.5 us at
+    // 1 GiB; four or more lose again below 1 GiB.
+    const int per_cta = tuning().sum_tiles > 0 ? tuning().sum_tiles : (tiles >= 8192 ? 2 : 1);
+    int64_t grid = ceil_div(ceil_div(tiles, per_cta), CL) * CL;
     const int64_t cap = static_cast<int64_t>(kSumMaxPartials) * CL;
     if (grid > cap) grid = cap;
     if (tuning().sum_trace != 0) {
@@ -1028,6 +1032,10 @@ int launch_rows_span_cfg(const float* x, int64_t rows, int64_t cols, typename R:
     if (st != FDL_OK) return st;
     int64_t rows_per_cta = (kRowSpanBytes - 32) / (cols * 4);
     if (rows_per_cta < 1) return FDL_ERR_UNSUPPORTED;
+    // A whole number of trips of the teams: 10 rows of 1001 floats over 8 teams would run a
+    // second trip with 2 teams at work.
+    constexpr int kTeams = kRowThreads / TPR;
+    if (rows_per_cta > kTeams) rows_per_cta -= rows_per_cta % kTeams;
     if (rows_per_cta > rows) rows_per_cta = rows;
     const int64_t grid = ceil_div(rows, rows_per_cta);
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;

@@ -531,8 +531,11 @@ int launch_masked_short_cfg(const RowParams& p, cudaStream_t stream) {
 // walk their rows float by float in shared memory -- consecutive lanes, consecutive floats --
 // and write the results back in place, and the whole CTA stores the run as 128-bit packs.  Only
 // the first and the last pack of the run can be shared with a neighbouring CTA's rows; those
-// two are stored one valid float at a time.  x and y must sit at the same phase.
-template <class Op, int TPR, int NVS>
+// two are stored one valid float at a time.  x and y must sit at the same phase.  The kernel
+// is bound by instruction issue (79% issue-active for layernorm on [1048576,63]), so EXTRAS
+// compiles the layernorm's optional gamma / beta / mean / rstd away when none is passed, and
+// the launcher gives a CTA a whole number of team trips.
+template <class Op, int TPR, int NVS, bool EXTRAS>
 __global__ void __launch_bounds__(256)
 rows_span_kernel(const RowParams p, int phase, int rows_per_cta) {
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
@@ -611,7 +614,7 @@ rows_span_kernel(const RowParams p, int phase, int rows_per_cta) {
         // Rows this short pay for every instruction per row: the reciprocal square root is the
         // hardware's approximate one (2 ulp), where the longer-row forms divide by sqrtf.
         const float scale = kSoftmax ? 1.0f / b : rsqrtf(b * inv_n + p.eps);
-        if (!kSoftmax && t == 0) {
+        if (!kSoftmax && EXTRAS && t == 0) {
             if (p.mean_out != nullptr) p.mean_out[r0 + i] = a;
             if (p.rstd_out != nullptr) p.rstd_out[r0 + i] = scale;
         }
@@ -620,7 +623,7 @@ rows_span_kernel(const RowParams p, int phase, int rows_per_cta) {
             const int c = t + k * TPR;
             if (c < p.cols) {
                 float o = kSoftmax ? v[k] * scale : (v[k] - a) * scale;
-                if (!kSoftmax) {
+                if (!kSoftmax && EXTRAS) {
                     if (p.gamma != nullptr) o *= __ldg(p.gamma + c);
                     if (p.beta != nullptr) o += __ldg(p.beta + c);
                 }
@@ -656,12 +659,22 @@ int launch_span_cfg(const RowParams& p, cudaStream_t stream) {
     const int phase = static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u);
     int64_t rows_per_cta = (kSpanBytes - 32) / (static_cast<int64_t>(p.cols) * 4);
     if (rows_per_cta < 1) return FDL_ERR_UNSUPPORTED;
+    // A whole number of trips of the 256 / TPR teams: 162 rows of 63 floats would leave the
+    // eleventh trip with 2 of 16 teams at work.
+    constexpr int kTeams = 256 / TPR;
+    if (rows_per_cta > kTeams) rows_per_cta -= rows_per_cta % kTeams;
     if (rows_per_cta > p.rows) rows_per_cta = p.rows;
     const int64_t grid = ceil_div(p.rows, rows_per_cta);
     if (grid > 2147483647) return FDL_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>((rows_per_cta * p.cols + 6) / 4 + 1) * 16;
-    return launch_ex(rows_span_kernel<Op, TPR, NVS>, dim3(static_cast<unsigned int>(grid)), dim3(256), smem, stream,
-                     dim3(1, 1, 1), tuning().pdl != 0, p, phase, static_cast<int>(rows_per_cta));
+    const bool extras = !std::is_same<Op, SoftmaxOp>::value &&
+                        (p.gamma != nullptr || p.beta != nullptr || p.mean_out != nullptr || p.rstd_out != nullptr);
+    const dim3 g(static_cast<unsigned int>(grid));
+    if (extras)
+        return launch_ex(rows_span_kernel<Op, TPR, NVS, true>, g, dim3(256), smem, stream, dim3(1, 1, 1),
+                         tuning().pdl != 0, p, phase, static_cast<int>(rows_per_cta));
+    return launch_ex(rows_span_kernel<Op, TPR, NVS, false>, g, dim3(256), smem, stream, dim3(1, 1, 1),
+                     tuning().pdl != 0, p, phase, static_cast<int>(rows_per_cta));
 }
 
 // Team size and values per lane for a row of `cols` floats (at most 256).
@@ -1152,23 +1165,76 @@ rows_staged_kernel(const RowParams p) {
 
 // ---- split form: rows longer than a cluster can hold -------------------------------------------
 //
-// Two kernels.  The first cuts every row into 32 KiB segments, one CTA each (grid = segments x
-// rows): the CTA keeps its segment in registers, leaves the segment's statistics in the
-// workspace -- softmax: (max, sum of exp(x - max)); layernorm: (mean, sum of squared
-// deviations from it) -- and the last CTA of a row to arrive (ticket counter) combines the
-// segments' statistics into the row's: softmax rescales each sum to the row maximum,
-// layernorm uses the pairwise update of Chan et al., both in a fixed order.  The second kernel
-// applies them elementwise.  Two reads and one write per element instead of one and one, against
-// the three passes (two of them out of L2 only while a row fits there) of the plain kernel.
+// Every row is cut into 32 KiB segments, one CTA each: the CTA keeps its segment in registers,
+// leaves the segment's statistics in the workspace -- softmax: (max, sum of exp(x - max));
+// layernorm: (mean, sum of squared deviations from it) -- and the last CTA of a row to arrive
+// (ticket counter) combines the segments' statistics into the row's: softmax rescales each sum to
+// the row maximum, layernorm uses the pairwise update of Chan et al., both in a fixed order.
+//
+// Two-kernel form: the first kernel ends with the statistics, a second one reads the rows again
+// and applies them -- two reads and one write per element from DRAM (by the time the second
+// kernel starts, the first has pushed the head of the tensor out of L2), against the three
+// passes of the plain kernel.
+//
+// One-kernel form (the default): both passes are tasks of ONE launch, and a segment is applied
+// `lag` rows after its statistics were taken, while it is still in L2 (the statistics pass loads
+// with an L2 evict-last hint, the apply pass with evict-first, stores are streaming).  Every CTA
+// first takes a ticket from a counter; tickets enumerate the nseg statistics tasks of row k
+// followed by the nseg apply tasks of row k - lag, row after row.  An apply task waits for the
+// row's statistics -- for tasks with SMALLER tickets, which CTAs that are already running hold (a
+// CTA takes its ticket when it starts) and which wait for nothing themselves, so the wait ends
+// whatever order the hardware starts CTAs in; it is bounded all the same.  A row's counter goes
+// 0 .. nseg (arrivals), nseg + 1 (statistics ready), .. 2 nseg + 1 (apply tasks done), and the
+// last task puts it back to 0.  The ticket counter is the last slot of the workspace's counter
+// block (rows use the others); its last taker zeroes it.  `lag` covers the 5-9 us from a
+// statistics task's start to the row's statistics (measured: a distance of 32-40 MB of rows is
+// needed before apply tasks stop stalling; less, and they hold CTA slots while they wait).
+//
+// The kernel reads every element once from DRAM (profiled on [128,524288]: 273 MB read for a
+// 268 MB tensor) but is bound by latency, not by DRAM (48-58% busy): a task is a chain of round
+// trips to L2 -- ticket, loads, publish or wait -- during which its CTA slot holds no load in flight.
+//
+// (Measured and dropped: persistent CTAs with a ring of 32 KiB shared-memory stages filled by
+// bulk-async copies a few tickets ahead, so that loads stay in flight while the threads reduce,
+// publish and wait: 2 CTAs x 3 stages per SM 41%, 3 CTAs x 2 stages 54% -- the per-task chain of
+// round trips is serial inside a CTA and fewer CTAs per SM run fewer chains at once.)
+//
+// (Measured and dropped: the CTAs of a row holding their segments in registers while they wait
+// for the row's statistics, a cluster in software of up to 296 CTAs, one read and one write per
+// element.  The chain load - reduce - publish - combine - flag - apply is ~10 us long and the
+// register file holds 19 MB: 46-54% of the copy bandwidth on [128,524288] and [256,262144],
+// against 56-67% for the two kernels.)
 
 constexpr int kSplitThreads = 256;
 constexpr int kSplitNV = 8;
 constexpr int kSplitSegVecs = kSplitThreads * kSplitNV;  // 2048 packs = 32 KiB
 constexpr int64_t kSplitMaxRows = kWorkspaceCounterBytes / 4;
+constexpr unsigned long long kSplitWaitNs = 2000000000ull;  // bounded wait of the one-kernel form
 
-// Both kernels address a row through the aligned packs of the flat buffer (RowEdges, as in the
+// The kernels address a row through the aligned packs of the flat buffer (RowEdges, as in the
 // masked form), so rows of any length and phase qualify; MASKED = false compiles the edge
 // handling away for rows that are whole packs.
+
+struct SplitSeg {
+    RowEdges edge;
+    int64_t first_pack;  // of the row, in the flat buffer
+    int voff;            // first pack of the segment, counted from the row's first
+    int local;           // packs of the row inside the segment
+};
+
+template <bool MASKED>
+__device__ __forceinline__ SplitSeg split_segment(const RowParams& p, int phase, int64_t row, int seg) {
+    SplitSeg sg;
+    const int64_t e0 = phase + row * p.cols;
+    sg.edge.head = MASKED ? static_cast<int>(e0 & 3) : 0;
+    sg.edge.cols = p.cols;
+    sg.edge.npk = (sg.edge.head + p.cols + 3) >> 2;
+    sg.first_pack = e0 >> 2;
+    sg.voff = seg * kSplitSegVecs;
+    sg.local = sg.edge.npk - sg.voff;
+    if (sg.local > kSplitSegVecs) sg.local = kSplitSegVecs;
+    return sg;
+}
 
 __device__ __forceinline__ int split_count(const RowEdges& e, int seg) {
     // floats of the row inside segment `seg`
@@ -1177,62 +1243,82 @@ __device__ __forceinline__ int split_count(const RowEdges& e, int seg) {
     return hi > lo ? hi - lo : 0;
 }
 
-template <class Op, bool MASKED>
-__global__ void __launch_bounds__(kSplitThreads)
-rows_split_stats_kernel(const RowParams p, int phase, float2* seg_stats, float2* row_stats,
-                        unsigned int* counters) {
-    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
-    constexpr float kLog2e = 1.4426950408889634f;
-    __shared__ float red[kMaxWarps];
-    __shared__ bool is_last;
-    const int64_t row = blockIdx.y;
-    const int seg = blockIdx.x;
-    const int nseg = gridDim.x;
-    const int64_t e0 = phase + row * p.cols;
-    RowEdges edge;
-    edge.head = MASKED ? static_cast<int>(e0 & 3) : 0;
-    edge.cols = p.cols;
-    edge.npk = (edge.head + p.cols + 3) >> 2;
-    const int voff = seg * kSplitSegVecs;
-    int local = edge.npk - voff;
-    if (local > kSplitSegVecs) local = kSplitSegVecs;
+// Loads with an L2 eviction-priority hint (policy from createpolicy).
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ float4 ld_hint(const float4* ptr, uint64_t policy) {
+    float4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(ptr), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ float ld_hint(const float* ptr, uint64_t policy) {
+    float v;
+    asm volatile("ld.global.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(ptr), "l"(policy));
+    return v;
+}
+
+// The segment into registers; lanes of an edge pack that belong to a neighbouring row get `neutral`.
+// HINT 0: streaming loads; 1: the lines are to stay in L2 (evict last); 2: they are not (evict first).
+template <bool MASKED, int HINT>
+__device__ __forceinline__ void split_load(const RowParams& p, int phase, const SplitSeg& sg, float neutral,
+                                           float4 (&v)[kSplitNV], int (&okv)[kSplitNV]) {
     const int t = threadIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + voff;
-    const float neutral = kSoftmax ? -INFINITY : 0.0f;
-    float4 v[kSplitNV];
-    int okv[kSplitNV];
+    uint64_t policy = 0;
+    if (HINT == 1) policy = l2_policy_evict_last();
+    if (HINT == 2) policy = l2_policy_evict_first();
+    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + sg.first_pack + sg.voff;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
         const int li = t + i * kSplitThreads;
-        okv[i] = li < local ? (MASKED ? edge.valid(voff + li) : 15) : 0;
-        if (li < local) {
+        okv[i] = li < sg.local ? (MASKED ? sg.edge.valid(sg.voff + li) : 15) : 0;
+        if (li < sg.local) {
             if (okv[i] == 15) {
-                v[i] = ld_stream(src + li);
+                v[i] = HINT == 0 ? ld_stream(src + li) : ld_hint(src + li, policy);
             } else {
                 v[i] = make_float4(neutral, neutral, neutral, neutral);
                 const float* q = reinterpret_cast<const float*>(src + li);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    if (okv[i] & (1 << k)) lane_of(v[i], k) = ld_stream(q + k);
+                    if (okv[i] & (1 << k)) lane_of(v[i], k) = HINT == 0 ? ld_stream(q + k) : ld_hint(q + k, policy);
                 }
             }
         }
     }
-    float a = neutral;
+}
+
+// The segment's statistics, in every thread.  Layernorm: foreign lanes of edge packs are moved
+// onto the segment mean on the way (they are never stored).
+template <class Op, bool MASKED>
+__device__ __forceinline__ float2 split_segment_stats(const SplitSeg& sg, int seg, float4 (&v)[kSplitNV],
+                                                      const int (&okv)[kSplitNV], float* red) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int t = threadIdx.x;
+    float a = kSoftmax ? -INFINITY : 0.0f;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
-        if (t + i * kSplitThreads < local) {
+        if (t + i * kSplitThreads < sg.local) {
             if (kSoftmax) a = fmaxf(a, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
             else a += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     }
-    const int count = split_count(edge, seg);
+    const int count = split_count(sg.edge, seg);
     if (kSoftmax) a = team_max<kSplitThreads, kSplitThreads>(a, red);
     else a = team_sum<kSplitThreads, kSplitThreads>(a, red) / static_cast<float>(count > 0 ? count : 1);
     float b = 0.0f;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
-        if (t + i * kSplitThreads < local) {
+        if (t + i * kSplitThreads < sg.local) {
             if (kSoftmax) {
                 b += (fast_exp2((v[i].x - a) * kLog2e) + fast_exp2((v[i].y - a) * kLog2e)) +
                      (fast_exp2((v[i].z - a) * kLog2e) + fast_exp2((v[i].w - a) * kLog2e));
@@ -1250,18 +1336,32 @@ rows_split_stats_kernel(const RowParams p, int phase, float2* seg_stats, float2*
     }
     b = team_sum<kSplitThreads, kSplitThreads>(b, red);
     if (kSoftmax && count == 0) b = 0.0f;  // an empty segment: exp(-inf - -inf) is not a number
+    return make_float2(a, b);
+}
+
+// Leaves the segment's statistics in the workspace; the last CTA of the row to arrive combines
+// them into row_stats[row].  SIGNAL: the row's counter is then set to nseg + 1 for the waiting
+// CTAs instead of back to 0.
+template <class Op, bool SIGNAL>
+__device__ __forceinline__ void split_publish(const RowParams& p, const SplitSeg& sg, int64_t row, int seg, int nseg,
+                                              float2 ab, float2* seg_stats, float2* row_stats, unsigned int* counters,
+                                              float* red, bool* is_last) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int t = threadIdx.x;
     if (t == 0) {
-        seg_stats[row * nseg + seg] = make_float2(a, b);
+        seg_stats[row * nseg + seg] = ab;
         __threadfence();
         const unsigned int ticket = atomicAdd(counters + row, 1u);
-        is_last = ticket == static_cast<unsigned int>(nseg - 1);
-        if (is_last) counters[row] = 0;
+        *is_last = ticket == static_cast<unsigned int>(nseg - 1);
+        if (*is_last && !SIGNAL) counters[row] = 0;
     }
     __syncthreads();
-    if (!is_last) return;
+    if (!*is_last) return;
     __threadfence();
-    // Combine the segments' statistics; thread k takes segments k, k + 256, ... in order.
+    // Thread k takes segments k, k + 256, ... in order.
     const float2* mine = seg_stats + row * nseg;
+    float2 result;
     if (kSoftmax) {
         float m = -INFINITY;
         for (int k = t; k < nseg; k += kSplitThreads) m = fmaxf(m, __ldcg(&mine[k].x));
@@ -1272,75 +1372,52 @@ rows_split_stats_kernel(const RowParams p, int phase, float2* seg_stats, float2*
             if (sk != 0.0f) s += sk * fast_exp2((__ldcg(&mine[k].x) - m) * kLog2e);
         }
         s = team_sum<kSplitThreads, kSplitThreads>(s, red);
-        if (t == 0) row_stats[row] = make_float2(m, 1.0f / s);
+        result = make_float2(m, 1.0f / s);
     } else {
         // mean = sum n_k mean_k / N;  M2 = sum (M2_k + n_k (mean_k - mean)^2)
         const float inv_n = 1.0f / static_cast<float>(p.cols);
         float s = 0.0f;
         for (int k = t; k < nseg; k += kSplitThreads) {
-            s += static_cast<float>(split_count(edge, k)) * __ldcg(&mine[k].x);
+            s += static_cast<float>(split_count(sg.edge, k)) * __ldcg(&mine[k].x);
         }
         const float mean = team_sum<kSplitThreads, kSplitThreads>(s, red) * inv_n;
         float q = 0.0f;
         for (int k = t; k < nseg; k += kSplitThreads) {
             const float d = __ldcg(&mine[k].x) - mean;
-            q += __ldcg(&mine[k].y) + static_cast<float>(split_count(edge, k)) * d * d;
+            q += __ldcg(&mine[k].y) + static_cast<float>(split_count(sg.edge, k)) * d * d;
         }
         const float var = team_sum<kSplitThreads, kSplitThreads>(q, red) * inv_n;
-        const float rstd = 1.0f / sqrtf(var + p.eps);
-        if (t == 0) {
-            row_stats[row] = make_float2(mean, rstd);
-            if (p.mean_out != nullptr) p.mean_out[row] = mean;
-            if (p.rstd_out != nullptr) p.rstd_out[row] = rstd;
+        result = make_float2(mean, 1.0f / sqrtf(var + p.eps));
+    }
+    if (t == 0) {
+        row_stats[row] = result;
+        if (!kSoftmax) {
+            if (p.mean_out != nullptr) p.mean_out[row] = result.x;
+            if (p.rstd_out != nullptr) p.rstd_out[row] = result.y;
+        }
+        if (SIGNAL) {
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(counters + row) = static_cast<unsigned int>(nseg) + 1u;
         }
     }
 }
 
+// y = the row's statistics applied to the segment in registers.
 template <class Op, bool MASKED>
-__global__ void __launch_bounds__(kSplitThreads)
-rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
+__device__ __forceinline__ void split_apply_store(const RowParams& p, int phase, const SplitSeg& sg, float2 st,
+                                                  const float4 (&v)[kSplitNV], const int (&okv)[kSplitNV]) {
     constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
     constexpr float kLog2e = 1.4426950408889634f;
-    const int64_t row = blockIdx.y;
-    const int64_t e0 = phase + row * p.cols;
-    RowEdges edge;
-    edge.head = MASKED ? static_cast<int>(e0 & 3) : 0;
-    edge.cols = p.cols;
-    edge.npk = (edge.head + p.cols + 3) >> 2;
-    const int voff = blockIdx.x * kSplitSegVecs;
-    int local = edge.npk - voff;
-    if (local > kSplitSegVecs) local = kSplitSegVecs;
     const int t = threadIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(p.x - phase) + (e0 >> 2) + voff;
-    float4* dst = reinterpret_cast<float4*>(p.y - phase) + (e0 >> 2) + voff;
-    float4 v[kSplitNV];
-    int okv[kSplitNV];
-#pragma unroll
-    for (int i = 0; i < kSplitNV; ++i) {
-        const int li = t + i * kSplitThreads;
-        okv[i] = li < local ? (MASKED ? edge.valid(voff + li) : 15) : 0;
-        if (li < local) {
-            if (okv[i] == 15) {
-                v[i] = ld_stream(src + li);
-            } else {
-                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float* q = reinterpret_cast<const float*>(src + li);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (okv[i] & (1 << k)) lane_of(v[i], k) = ld_stream(q + k);
-                }
-            }
-        }
-    }
-    const float2 st = row_stats[row];
+    float4* dst = reinterpret_cast<float4*>(p.y - phase) + sg.first_pack + sg.voff;
     const bool affine = !kSoftmax && (p.gamma != nullptr || p.beta != nullptr);
     // gamma / beta line up with the packs (and can be read 128 bits at a time)
-    const bool affine_packs = (!MASKED || edge.head == 0) &&
+    const bool affine_packs = (!MASKED || sg.edge.head == 0) &&
                               ((reinterpret_cast<uintptr_t>(p.gamma) | reinterpret_cast<uintptr_t>(p.beta)) & 15u) == 0;
 #pragma unroll
     for (int i = 0; i < kSplitNV; ++i) {
         const int li = t + i * kSplitThreads;
-        if (li < local) {
+        if (li < sg.local) {
             float4 o;
             if (kSoftmax) {
                 o = make_float4(fast_exp2((v[i].x - st.x) * kLog2e) * st.y, fast_exp2((v[i].y - st.x) * kLog2e) * st.y,
@@ -1349,7 +1426,7 @@ rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
                 o = make_float4((v[i].x - st.x) * st.y, (v[i].y - st.x) * st.y, (v[i].z - st.x) * st.y,
                                 (v[i].w - st.x) * st.y);
                 if (affine) {
-                    const int c0 = (voff + li) * 4 - edge.head;
+                    const int c0 = (sg.voff + li) * 4 - sg.edge.head;
                     if (affine_packs && okv[i] == 15) {
                         if (p.gamma != nullptr) {
                             const float4 g = __ldg(reinterpret_cast<const float4*>(p.gamma + c0));
@@ -1384,6 +1461,137 @@ rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
 }
 
 template <class Op, bool MASKED>
+__global__ void __launch_bounds__(kSplitThreads, MASKED ? 4 : 5)
+rows_split_stats_kernel(const RowParams p, int phase, float2* seg_stats, float2* row_stats,
+                        unsigned int* counters) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    __shared__ float red[kMaxWarps];
+    __shared__ bool is_last;
+    const int64_t row = blockIdx.y;
+    const int seg = blockIdx.x;
+    const SplitSeg sg = split_segment<MASKED>(p, phase, row, seg);
+    float4 v[kSplitNV];
+    int okv[kSplitNV];
+    split_load<MASKED, 0>(p, phase, sg, kSoftmax ? -INFINITY : 0.0f, v, okv);
+    const float2 ab = split_segment_stats<Op, MASKED>(sg, seg, v, okv, red);
+    split_publish<Op, false>(p, sg, row, seg, gridDim.x, ab, seg_stats, row_stats, counters, red, &is_last);
+}
+
+template <class Op, bool MASKED>
+__global__ void __launch_bounds__(kSplitThreads, MASKED ? 4 : 5)
+rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
+    const int64_t row = blockIdx.y;
+    const SplitSeg sg = split_segment<MASKED>(p, phase, row, blockIdx.x);
+    float4 v[kSplitNV];
+    int okv[kSplitNV];
+    split_load<MASKED, 0>(p, phase, sg, 0.0f, v, okv);
+    split_apply_store<Op, MASKED>(p, phase, sg, row_stats[row], v, okv);
+}
+
+// The one-kernel form.  Tickets enumerate: the statistics tasks of rows 0 .. lag-1; then, for
+// row k = lag .. rows-1, the statistics tasks of row k followed by the apply tasks of row
+// k - lag; then the apply tasks of the last lag rows.  HINTS = false uses plain streaming loads
+// in both passes (tuning key rows_split_hints = 0, for comparison).
+struct SplitPlan {
+    int nseg;
+    int lag;
+    unsigned int head;    // tickets before the first apply task: lag * nseg
+    unsigned int middle;  // tickets of the rounds that hold both kinds: (rows - lag) * 2 * nseg
+};
+
+template <class Op, bool MASKED, bool HINTS>
+__global__ void __launch_bounds__(kSplitThreads, (MASKED || !std::is_same<Op, SoftmaxOp>::value) ? 4 : 5)
+rows_split_pipelined_kernel(const RowParams p, int phase, const SplitPlan plan, float2* seg_stats, float2* row_stats,
+                            unsigned int* counters) {
+    constexpr bool kSoftmax = std::is_same<Op, SoftmaxOp>::value;
+    __shared__ float red[kMaxWarps];
+    __shared__ bool is_last;
+    __shared__ unsigned int ticket_shared;
+    const int t = threadIdx.x;
+    pdl_wait();  // the input may be the previous kernel's output
+    unsigned int* queue = counters + (kSplitMaxRows - 1);
+    if (t == 0) {
+        ticket_shared = atomicAdd(queue, 1u);
+        if (ticket_shared == gridDim.x - 1) *queue = 0;
+    }
+    __syncthreads();
+    const unsigned int ticket = ticket_shared;
+    const unsigned int n = static_cast<unsigned int>(plan.nseg);
+    int64_t row;
+    int seg;
+    bool apply;
+    if (ticket < plan.head) {
+        row = ticket / n;
+        seg = static_cast<int>(ticket % n);
+        apply = false;
+    } else if (ticket < plan.head + plan.middle) {
+        const unsigned int u = ticket - plan.head;
+        const unsigned int k = u / (2u * n), j = u % (2u * n);
+        apply = j >= n;
+        row = apply ? k : static_cast<int64_t>(k) + plan.lag;
+        seg = static_cast<int>(apply ? j - n : j);
+    } else {
+        const unsigned int u = ticket - plan.head - plan.middle;
+        row = p.rows - plan.lag + u / n;
+        seg = static_cast<int>(u % n);
+        apply = true;
+    }
+    const SplitSeg sg = split_segment<MASKED>(p, phase, row, seg);
+    float4 v[kSplitNV];
+    int okv[kSplitNV];
+    if (!apply) {
+        split_load<MASKED, HINTS ? 1 : 0>(p, phase, sg, kSoftmax ? -INFINITY : 0.0f, v, okv);
+        const float2 ab = split_segment_stats<Op, MASKED>(sg, seg, v, okv, red);
+        split_publish<Op, true>(p, sg, row, seg, plan.nseg, ab, seg_stats, row_stats, counters, red, &is_last);
+        return;
+    }
+    split_load<MASKED, HINTS ? 2 : 0>(p, phase, sg, 0.0f, v, okv);  // in flight while thread 0 waits
+    bool ready = true;
+    if (t == 0) {
+        const volatile unsigned int* flag = counters + row;
+        const unsigned long long t0 = timer_ns();
+        unsigned int polls = 0;
+        while (*flag <= n) {
+            if ((++polls & 63u) == 0 && timer_ns() - t0 > kSplitWaitNs) {
+                ready = false;
+                break;
+            }
+        }
+        __threadfence();
+    }
+    ready = __syncthreads_and(ready);
+    if (ready) split_apply_store<Op, MASKED>(p, phase, sg, __ldcg(row_stats + row), v, okv);
+    if (t == 0) {
+        if (!ready) atomicOr(p.error_flag, 4u);
+        const unsigned int before = atomicAdd(counters + row, 1u);
+        if (before == 2u * n) counters[row] = 0;  // the row's last task
+    }
+}
+
+constexpr int64_t kSplitLagBytes = 36ll << 20;
+
+template <class Op, bool MASKED>
+int launch_rows_split_pipelined(const RowParams& p, int phase, int64_t nseg, float2* seg_stats, float2* row_stats,
+                                unsigned int* counters, cudaStream_t stream) {
+    int64_t lag = tuning().rows_split_lag > 0 ? tuning().rows_split_lag
+                                              : ceil_div(kSplitLagBytes, static_cast<int64_t>(p.cols) * 4);
+    if (lag > p.rows) lag = p.rows;
+    const int64_t tasks = 2 * p.rows * nseg;
+    if (tasks > 2147483647 || p.rows >= kSplitMaxRows) return FDL_ERR_UNSUPPORTED;
+    SplitPlan plan;
+    plan.nseg = static_cast<int>(nseg);
+    plan.lag = static_cast<int>(lag);
+    plan.head = static_cast<unsigned int>(lag * nseg);
+    plan.middle = static_cast<unsigned int>((p.rows - lag) * 2 * nseg);
+    const dim3 grid(static_cast<unsigned int>(tasks));
+    if (tuning().rows_split_hints != 0)
+        return launch_ex(rows_split_pipelined_kernel<Op, MASKED, true>, grid, dim3(kSplitThreads), 0, stream, dim3(1, 1, 1),
+                         tuning().pdl != 0, p, phase, plan, seg_stats, row_stats, counters);
+    return launch_ex(rows_split_pipelined_kernel<Op, MASKED, false>, grid, dim3(kSplitThreads), 0, stream, dim3(1, 1, 1),
+                     tuning().pdl != 0, p, phase, plan, seg_stats, row_stats, counters);
+}
+
+template <class Op, bool MASKED>
 int launch_rows_split(const RowParams& p, cudaStream_t stream) {
     const int phase = MASKED ? static_cast<int>((reinterpret_cast<uintptr_t>(p.x) & 15u) / 4u) : 0;
     const int64_t npk = MASKED ? (static_cast<int64_t>(p.cols) + 6) / 4 : p.cols / 4;
@@ -1396,6 +1604,11 @@ int launch_rows_split(const RowParams& p, cudaStream_t stream) {
     unsigned int* counters = static_cast<unsigned int*>(scratch);
     float2* row_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes);
     float2* seg_stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + kWorkspaceCounterBytes + row_bytes);
+    if (tuning().rows_split_fused != 0) {
+        const int st = launch_rows_split_pipelined<Op, MASKED>(p, phase, nseg, seg_stats, row_stats, counters, stream);
+        if (st != FDL_ERR_UNSUPPORTED) return st;
+    }
+    if (p.rows > 65535) return FDL_ERR_UNSUPPORTED;
     const dim3 grid(static_cast<unsigned int>(nseg), static_cast<unsigned int>(p.rows));
     rows_split_stats_kernel<Op, MASKED><<<grid, kSplitThreads, 0, stream>>>(p, phase, seg_stats, row_stats, counters);
     int st = launch_status();
@@ -1555,6 +1768,9 @@ int launch_rows_op(RowParams p, cudaStream_t stream) {
     const bool same_phase = ((reinterpret_cast<uintptr_t>(p.x) ^ reinterpret_cast<uintptr_t>(p.y)) & 15u) == 0;
     // Rows beyond 65536 floats (beyond 16384 when they do not consist of whole aligned packs):
     // the row in a cluster's shared memory, read once.
+    if (tuning().rows_split_from > 0 && p.cols >= tuning().rows_split_from && same_phase && p.rows < kSplitMaxRows) {
+        return packs ? launch_rows_split<Op, false>(p, stream) : launch_rows_split<Op, true>(p, stream);
+    }
     const int smem_from = tuning().rows_smem_from > 0 ? tuning().rows_smem_from : 4 * kCtaMaxCols;
     if (tuning().rows_smem != 0 && same_phase && (packs ? p.cols > smem_from : p.cols + 6 > kCtaMaxCols)) {
         const int st = launch_rows_smem<Op>(p, info, stream);

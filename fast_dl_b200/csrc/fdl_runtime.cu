@@ -163,6 +163,26 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().sum_cluster = value;
         return FDL_OK;
     }
+    if (k == "rows_split_from" && value >= 0) {
+        fdl::tuning().rows_split_from = value;
+        return FDL_OK;
+    }
+    if (k == "rows_split_lag" && value >= 0 && value <= 4096) {
+        fdl::tuning().rows_split_lag = value;
+        return FDL_OK;
+    }
+    if (k == "rows_split_hints" && (value == 0 || value == 1)) {
+        fdl::tuning().rows_split_hints = value;
+        return FDL_OK;
+    }
+    if (k == "rows_split_fused" && (value == 0 || value == 1)) {
+        fdl::tuning().rows_split_fused = value;
+        return FDL_OK;
+    }
+    if (k == "sum_tiles" && value >= 0 && value <= 64) {
+        fdl::tuning().sum_tiles = value;
+        return FDL_OK;
+    }
     if (k == "cols_tx" && (value == 16 || value == 32 || value == 64 || value == 128 || value == 256)) {
         fdl::tuning().cols_tx = value;
         return FDL_OK;

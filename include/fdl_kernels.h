@@ -103,7 +103,15 @@ int fdl_take_device_error(void);
 
 /* Measurement aid: selects a launch shape so that a bench can show, on the same build,
  * why the default was chosen.  Keys: "sum_cluster" (1, 2, 4 or 8 CTAs per cluster in the
- * full sum; default 4), "rows_staged" (0 = softmax/layernorm rows loaded straight into
+ * full sum; default 4), "rows_split_fused" (softmax/layernorm rows longer than a
+ * cluster holds: 1 = one kernel whose statistics and apply tasks are pipelined through L2,
+ * 0 = two kernels, the rows read twice from DRAM; default 1), "rows_split_lag" (rows between a
+ * row's statistics and its apply tasks in that kernel, 1..4096; 0 = 36 MiB of rows; default 0),
+ * "rows_split_hints" (1 = L2 eviction-priority hints on that kernel's loads, 0 = plain streaming
+ * loads; default 1), "rows_split_from" (> 0: rows of at least this many floats take the split
+ * form instead of the cluster forms; default 0),
+ * "sum_tiles" (32 KiB tiles a CTA of the full sum walks, 1..64; 0 = two
+ * from 256 MiB on, one below; default 0; applies to every full-sum entry point), "rows_staged" (0 = softmax/layernorm rows loaded straight into
  * registers, 1 = staged through shared memory by one bulk-async copy per CTA, -1 = staged
  * for rows of up to 128 floats and direct beyond; default -1), "rows_warp16" (rows of
  * 1028..2048 floats: 1 = one warp per row with 16 packs a lane, 0 = a 256-thread CTA per row,

@@ -192,6 +192,48 @@ def test_shared_memory_cluster_form_agrees_with_the_other_forms(fdl, cuda, rows,
     assert_close_scaled(out[1][1], out[0][1], "layernorm: shared-memory form vs the other forms")
 
 
+@pytest.mark.parametrize("rows,cols", [(1, 131076), (2, 524288), (3, 300001), (41, 140000), (67, 131077), (300, 132000),
+                                       (5, 2100004)])
+@pytest.mark.parametrize("lag,hints", [(0, 1), (1, 1), (3, 0)])
+def test_one_kernel_form_of_rows_longer_than_a_cluster_equals_the_two_kernel_form(fdl, cuda, rows, cols, lag, hints):
+    """Rows beyond 131072 floats.  The default takes the statistics of a row and applies them in
+    ONE launch, the apply tasks a few rows behind so that they read from L2.  It gives the bits of
+    the two-kernel form (tuning key rows_split_fused = 0) at any lag, with and without the L2
+    hints, leaves no device error, and leaves the shared counters at zero: a second call, and
+    the other ops that use the counters, still answer right."""
+    rng = np.random.default_rng(rows * 1000003 + cols)
+    x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+    g = rng.uniform(0.9, 1.1, cols).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, cols).astype(np.float32)
+    xd, gd, bd = dev(cuda, x), dev(cuda, g), dev(cuda, b)
+    out = {}
+    for fused in (1, 0, 1):
+        fdl.set_tuning("rows_split_fused", fused)
+        fdl.set_tuning("rows_split_lag", lag)
+        fdl.set_tuning("rows_split_hints", hints)
+        try:
+            sm = to_np(fdl.softmax_rows(xd))
+            ln, mean, rstd = (to_np(t) for t in fdl.layernorm_rows(xd, gd, bd, want_stats=True))
+        finally:
+            fdl.set_tuning("rows_split_fused", 1)
+            fdl.set_tuning("rows_split_lag", 0)
+            fdl.set_tuning("rows_split_hints", 1)
+        if fused in out:
+            for first, again in zip(out[fused], (sm, ln, mean, rstd)):
+                assert np.array_equal(first, again)
+        out[fused] = (sm, ln, mean, rstd)
+    fdl.take_device_error()  # raises if a bounded wait ran out
+    for one, two in zip(out[1], out[0]):
+        assert np.array_equal(one, two)
+    assert_close_scaled(out[1][0], orc.softmax_rows_f64(x), "softmax vs fp64")
+    assert_close_scaled(out[1][1], orc.layernorm_rows_f64(x, g, b, 1e-5), "layernorm vs fp64")
+    # the column reduction and the full sum share the counter block
+    col = to_np(fdl.reduce_cols(xd, fdl.REDUCE_SUM))
+    assert np.abs(col - x.astype(np.float64).sum(axis=0)).max() <= 1e-4 * max(1.0, np.abs(x).sum(axis=0).max())
+    total = float(to_np(fdl.full_sum(xd)).reshape(-1)[0])
+    assert abs(total - x.astype(np.float64).sum()) <= 1e-5 * np.abs(x).sum()
+
+
 @pytest.mark.parametrize("rows,cols", [(64, 1024), (100, 1001), (1000, 63), (7, 4096), (9, 8190), (5, 16380),
                                        (3, 40001), (2, 20000), (2, 140002), (3, 65537), (2, 460001)])
 @pytest.mark.parametrize("x_off,y_off", [(1, 1), (3, 3), (2, 2), (1, 2), (0, 1)])
