@@ -44,6 +44,7 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // (set through fdl_set_tuning).  Defaults are the measured best on B200.
 struct Tuning {
     int sum_cluster = 4;   // CTAs per cluster in the full sum (1 = no cluster stage)
+    int rows_span_argmax_from = 65;  // argmax along axis 1 of odd rows takes the span form from this many floats on
     int rows_split_from = 0;   // > 0: rows of at least this many floats take the split form whatever the other forms offer
     int rows_split_fused = 1;  // rows beyond a cluster's reach: 1 = one kernel, statistics and apply tasks pipelined through L2; 0 = two kernels
     int rows_split_lag = 0;    // rows between a row's statistics and its apply tasks in that kernel (0 = 36 MiB of rows)

@@ -488,7 +488,15 @@ struct SumRed {
     __device__ static State identity() { return 0.0f; }
     __device__ static State lift(float v, int) { return v; }
     __device__ static State combine(State a, State b) { return a + b; }
+    // a chain that visits its columns in increasing order takes the next one
+    __device__ static State combine_next(State a, float v, int) { return a + v; }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    template <int TPR>
+    __device__ static State team_reduce(State s) {  // over aligned groups of TPR lanes, every lane of the warp calling
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(kFullMask, s, o);
+        return s;
+    }
     __device__ static State load_cg(const State* p) { return __ldcg(p); }  // L2, never a stale L1 line
     __device__ static State shift(State a, int) { return a; }
     __device__ static Out finish(State a, int64_t, float) { return a; }
@@ -503,7 +511,14 @@ struct MaxRed {
     __device__ static State identity() { return -INFINITY; }
     __device__ static State lift(float v, int) { return v; }
     __device__ static State combine(State a, State b) { return fmaxf(a, b); }
+    __device__ static State combine_next(State a, float v, int) { return fmaxf(a, v); }
     __device__ static State shuffle_xor(State a, int o) { return __shfl_xor_sync(kFullMask, a, o); }
+    template <int TPR>
+    __device__ static State team_reduce(State s) {
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) s = fmaxf(s, __shfl_xor_sync(kFullMask, s, o));
+        return s;
+    }
     __device__ static State load_cg(const State* p) { return __ldcg(p); }
     __device__ static State shift(State a, int) { return a; }
     __device__ static Out finish(State a, int64_t, float) { return a; }
@@ -524,8 +539,30 @@ struct ArgmaxRed {
         const bool take_b = (b.v > a.v) || (b.v == a.v && b.i < a.i);
         return take_b ? b : a;
     }
+    // The next (higher) column of a chain wins only if it is strictly greater, so no index is
+    // compared; fmaxf drops a NaN for -inf.
+    __device__ static State combine_next(State a, float v, int col) {
+        v = fmaxf(v, -INFINITY);
+        const bool take = v > a.v;
+        return ArgState{take ? v : a.v, take ? col : a.i};
+    }
     __device__ static State shuffle_xor(State a, int o) {
         return ArgState{__shfl_xor_sync(kFullMask, a.v, o), __shfl_xor_sync(kFullMask, a.i, o)};
+    }
+    // The team's maximum and the lowest column that holds it, by two warp-wide integer reductions
+    // (redux.sync) instead of a shuffle tree on (value, column) pairs.  The float is mapped onto
+    // an integer of the same order; -0 and +0 share a key, as they compare equal.  s.v is never NaN.
+    template <int TPR>
+    __device__ static State team_reduce(State s) {
+        const unsigned int lane = threadIdx.x & (kWarp - 1);
+        const unsigned int mask = TPR == kWarp ? kFullMask : ((1u << TPR) - 1u) << (lane & ~static_cast<unsigned int>(TPR - 1));
+        int key = __float_as_int(s.v);
+        key ^= (key >> 31) & 0x7fffffff;
+        if (s.v == 0.0f) key = 0;
+        const int best = __reduce_max_sync(mask, key);
+        const int col = __reduce_min_sync(mask, key == best ? s.i : INT_MAX);
+        int bits = best ^ ((best >> 31) & 0x7fffffff);
+        return ArgState{__int_as_float(bits), col};
     }
     __device__ static State load_cg(const State* p) { return ArgState{__ldcg(&p->v), __ldcg(&p->i)}; }
     // columns counted from the start of the row's first pack -> columns of the row
@@ -642,14 +679,25 @@ __device__ __forceinline__ typename R::State thread_reduce_flat(const float* x, 
     const int full_hi = tail ? npk - 1 : npk;
     const int lo = full_lo > pk_begin ? full_lo : pk_begin;
     const int hi = full_hi < pk_end ? full_hi : pk_end;
-    State s = thread_reduce_span<R, 4, STRIDE>(line, lo + t, hi);
+    // The edge floats (at most three, in lane 0 for the head and lane 1 for the tail) are
+    // requested before the packs, so that they arrive along with them.
+    float edge[3];
+    int edge_col = 0, edge_n = 0;
     if (t == 0 && head && pk_begin == 0) {
-        const int stop = head + cols < 4 ? head + cols : 4;
-        for (int k = head; k < stop; ++k) s = R::combine(s, R::lift(ld_stream(line + k), k));
+        edge_col = head;
+        edge_n = (head + cols < 4 ? head + cols : 4) - head;
+    } else if (t == 1 && tail && !(npk == 1 && head) && npk - 1 >= pk_begin && npk - 1 < pk_end) {
+        edge_col = (npk - 1) * 4;
+        edge_n = tail;
     }
-    if (t == 1 && tail && !(npk == 1 && head) && npk - 1 >= pk_begin && npk - 1 < pk_end) {
-        const int base = (npk - 1) * 4;
-        for (int k = 0; k < tail; ++k) s = R::combine(s, R::lift(ld_stream(line + base + k), base + k));
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        if (k < edge_n) edge[k] = ld_stream(line + edge_col + k);
+    }
+    State s = thread_reduce_span<R, 4, STRIDE>(line, lo + t, hi);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        if (k < edge_n) s = R::combine(s, R::lift(edge[k], edge_col + k));
     }
     *head_out = head;
     return s;
@@ -1009,17 +1057,21 @@ reduce_rows_span_kernel(const float* x, int64_t rows, int cols, typename R::Out*
 #pragma unroll
         for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::identity();
         if (active) {
-            for (int c = t; c < cols; c += TPR * kRowUnroll) {
+            // whole trips of the team without a bounds check (the same number for every lane),
+            // then one checked trip
+            int c = t;
+            for (int covered = TPR * kRowUnroll; covered <= cols; covered += TPR * kRowUnroll, c += TPR * kRowUnroll) {
 #pragma unroll
-                for (int u = 0; u < kRowUnroll; ++u) {
-                    const int cc = c + u * TPR;
-                    if (cc < cols) acc[u] = R::combine(acc[u], R::lift(rowp[cc], cc));
-                }
+                for (int u = 0; u < kRowUnroll; ++u) acc[u] = R::combine_next(acc[u], rowp[c + u * TPR], c + u * TPR);
+            }
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                const int cc = c + u * TPR;
+                if (cc < cols) acc[u] = R::combine_next(acc[u], rowp[cc], cc);
             }
         }
         State s = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
-#pragma unroll
-        for (int o = TPR / 2; o > 0; o >>= 1) s = R::combine(s, R::shuffle_xor(s, o));
+        s = R::template team_reduce<TPR>(s);
         if (active && t == 0) out[r0 + i] = R::finish(s, cols, divisor);
     }
 }
@@ -1063,7 +1115,8 @@ int launch_rows(const float* x, int64_t rows, int64_t cols, typename R::Out* out
     const bool vec = aligned16(x) && cols % 4 == 0;
     // (argmax on rows of up to 64 floats stays with the team kernels: its (value, index) pairs
     // cost two shuffles a step and the span form measured 50% against 60% on [1048576,63])
-    if (!vec && cols <= tuning().rows_span_reduce_cols && cols <= kRowSpanMaxCols && !(R::kIsArgmax && cols <= 64)) {
+    if (!vec && cols <= tuning().rows_span_reduce_cols && cols <= kRowSpanMaxCols &&
+        !(R::kIsArgmax && cols < tuning().rows_span_argmax_from)) {
         const int st = launch_rows_span<R>(x, rows, cols, out, stream);
         if (st != FDL_ERR_UNSUPPORTED) return st;
     }

@@ -163,6 +163,10 @@ int fdl_set_tuning(const char* key, int value) {
         fdl::tuning().sum_cluster = value;
         return FDL_OK;
     }
+    if (k == "rows_span_argmax_from" && value >= 1) {
+        fdl::tuning().rows_span_argmax_from = value;
+        return FDL_OK;
+    }
     if (k == "rows_split_from" && value >= 0) {
         fdl::tuning().rows_split_from = value;
         return FDL_OK;

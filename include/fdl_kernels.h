@@ -118,7 +118,8 @@ int fdl_take_device_error(void);
  * -1 = whichever measured faster for the op and length; default -1), "rows_cluster_threads"
  * (256 or 512 threads per CTA in the cluster form of rows of 16388..65536 floats; default 256),
  * "rows_span_reduce_cols" (the same for the row reductions sum / mean / max / argmax along axis 1;
- * 0..2048, default 2048),
+ * 0..2048, default 2048), "rows_span_argmax_from" (argmax along axis 1 takes that form from rows
+ * of this many floats on; default 65),
  * "rows_span_cols" (rows of up to this many floats whose length is not a multiple of 4, or whose
  * base is off the 16-byte grid, are staged as runs of rows through shared memory; 0..256, default 256),
  * "rows_smem" (1 = rows beyond 65536 floats, or beyond 16384 at odd lengths, are kept in a

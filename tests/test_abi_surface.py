@@ -59,7 +59,7 @@ def test_every_documented_tuning_key_is_accepted(fdl):
     header = (ROOT / "include" / "fdl_kernels.h").read_text()
     doc = header[header.index("Measurement aid: selects a launch shape"):header.index("int fdl_set_tuning")]
     keys = re.findall(r'"([a-z0-9_]+)"', doc)
-    defaults = {"sum_cluster": 4, "sum_tiles": 0, "rows_split_fused": 1, "rows_split_lag": 0, "rows_split_hints": 1, "rows_split_from": 0, "rows_staged": -1, "rows_warp16": -1, "rows_cluster_threads": 256, "rows_span_cols": 256, "rows_span_reduce_cols": 2048, "rows_smem": 1, "rows_smem_cluster": 0, "rows_smem_from": 0,
+    defaults = {"sum_cluster": 4, "sum_tiles": 0, "rows_split_fused": 1, "rows_split_lag": 0, "rows_split_hints": 1, "rows_split_from": 0, "rows_staged": -1, "rows_warp16": -1, "rows_cluster_threads": 256, "rows_span_cols": 256, "rows_span_reduce_cols": 2048, "rows_span_argmax_from": 65, "rows_smem": 1, "rows_smem_cluster": 0, "rows_smem_from": 0,
                 "cols_tx": 64, "cols_cluster": 0, "cols_ctas_per_sm": 4, "cols_chunks": 0, "cols_single": 1, "cols_regroup": 1,
                 "pdl": 1, "bcast2d": 1, "bcast2d_rows": 0, "exchange_wait_ms": 2000, "sum_trace": 0}
     assert sorted(keys) == sorted(defaults), keys

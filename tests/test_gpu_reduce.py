@@ -118,6 +118,29 @@ def test_argmax_ties_nan_inf(fdl, cuda):
         np.testing.assert_array_equal(got, orc.argmax_rows(y))
         assert got[1] == 0 and got[2] == 0 and got[0] == shape[1] - 1
         assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, y), fdl.REDUCE_MAX)), orc.reduce_rows(y, 2), f"max {shape}")
+    for shape in ((3000, 7), (2000, 63), (1000, 129), (700, 255), (300, 1001), (40, 2047), (9, 8191)):  # odd lengths
+        y = rng.integers(0, 4, size=shape).astype(np.float32)
+        y[1, :] = np.nan
+        y[2, :] = -np.inf
+        y[3, ::3] = np.nan
+        y[0, shape[1] - 1] = np.inf
+        y[4, :] = -3.0
+        y[4, 2], y[4, shape[1] - 2] = -0.0, 0.0     # equal as floats: the lower column wins
+        y[5, :] = -np.inf
+        y[5, shape[1] - 1] = -1e30
+        y[6, :] = np.nan
+        y[6, 5] = -np.inf                           # NaN ranks as -inf: column 0
+        for tune in (65, 1):                        # short rows: the team kernels, then the span form
+            fdl.set_tuning("rows_span_argmax_from", tune)
+            try:
+                got = to_np(fdl.argmax_rows(dev(cuda, y)))
+            finally:
+                fdl.set_tuning("rows_span_argmax_from", 65)
+            np.testing.assert_array_equal(got, orc.argmax_rows(y))
+            assert got[1] == 0 and got[2] == 0 and got[0] == shape[1] - 1 and got[4] == 2
+            assert got[5] == shape[1] - 1 and got[6] == 0
+        y[4, 2] = 0.0   # (the sign of a zero maximum is whatever fmaxf makes of the order of evaluation)
+        assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, y), fdl.REDUCE_MAX)), orc.reduce_rows(y, 2), f"max {shape}")
     small = rng.integers(0, 3, size=(1000, 37)).astype(np.float32)
     np.testing.assert_array_equal(to_np(fdl.argmax_rows(dev(cuda, small))), orc.argmax_rows(small))
     assert_bit_exact(to_np(fdl.reduce_rows(dev(cuda, x), fdl.REDUCE_MAX)), orc.reduce_rows(x, 2), "max with nan")
