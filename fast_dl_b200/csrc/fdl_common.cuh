@@ -82,6 +82,7 @@ Tuning& tuning();
 // Per-device workspace the library owns (allocated on first use, grown on demand,
 // never freed before process exit).  Used when a caller passes scratch == NULL.
 int get_workspace(size_t bytes, void** out);
+void reset_workspace_counters();  // zeroes the counter block of every device's workspace
 // Every user of the workspace keeps its arrival counters in the first 64 KiB (zero between
 // launches) and its partial results behind them.
 constexpr int kWorkspaceCounterBytes = 65536;

@@ -123,6 +123,24 @@ int get_workspace(size_t bytes, void** out) {
     return FDL_OK;
 }
 
+// Zeroes the counter block of every device's workspace (the caller has synchronised).
+void reset_workspace_counters() {
+    int current = 0;
+    if (cudaGetDevice(&current) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (int dev = 0; dev < kMaxDevices; ++dev) {
+        Workspace& ws = g_workspace[dev];
+        if (ws.ptr == nullptr || ws.bytes < static_cast<size_t>(kWorkspaceCounterBytes)) continue;
+        if (cudaSetDevice(dev) != cudaSuccess || cudaMemset(ws.ptr, 0, kWorkspaceCounterBytes) != cudaSuccess) {
+            cudaGetLastError();
+        }
+    }
+    cudaSetDevice(current);
+}
+
 }  // namespace fdl
 
 extern "C" {
@@ -153,7 +171,11 @@ const char* fdl_error_string(int status) {
 }
 
 int fdl_take_device_error(void) {
-    return fdl::read_and_clear_device_error_flag() != 0 ? FDL_ERR_DEVICE_WAIT : FDL_OK;
+    if (fdl::read_and_clear_device_error_flag() == 0) return FDL_OK;
+    // A kernel that gave up a wait may have left arrival counters half-way; the kernels that
+    // share them expect zeros.
+    fdl::reset_workspace_counters();
+    return FDL_ERR_DEVICE_WAIT;
 }
 
 int fdl_set_tuning(const char* key, int value) {

@@ -98,7 +98,9 @@ int fdl_stream_synchronize(void* stream);
 /* Kernels that wait on the copy engine bound every wait; one that gives up raises a
  * flag in host-visible memory instead of spinning.  This returns FDL_ERR_DEVICE_WAIT if
  * the flag was raised since the last call (and clears it), else FDL_OK.  Meaningful
- * after the stream has been synchronised. */
+ * after the stream has been synchronised; when it reports a wait that ran out it also
+ * zeroes the arrival counters in the library's own workspace, which a kernel that gave up
+ * may have left half-way, so the calls that follow start clean. */
 int fdl_take_device_error(void);
 
 /* Measurement aid: selects a launch shape so that a bench can show, on the same build,
