@@ -67,6 +67,32 @@ def test_no_device_memory_is_taken(fdl, cuda):
     assert out.item() == float(1 << 22)
 
 
+def test_static_entry_in_a_cuda_graph_after_one_eager_call(fdl, cuda):
+    """After one eager call (which looks up the array's address for the device) the call is a
+    memset node and a kernel node: captured once, replayed on changed data, it follows the data."""
+    x = cuda.full((1 << 22,), 0.5, dtype=cuda.float32, device="cuda")
+    out = cuda.zeros(1, dtype=cuda.float32, device="cuda")
+    out64 = cuda.zeros(1, dtype=cuda.float64, device="cuda")
+    fdl.check(fdl.lib().fdl_sum_f32_static(x.data_ptr(), x.numel(), out.data_ptr(), out64.data_ptr(), None), "eager")
+    cuda.cuda.synchronize()
+    assert out.item() == 0.5 * (1 << 22)
+    side = cuda.cuda.Stream()
+    side.wait_stream(cuda.cuda.current_stream())
+    graph = cuda.cuda.CUDAGraph()
+    with cuda.cuda.stream(side):
+        with cuda.cuda.graph(graph, stream=side):
+            fdl.check(fdl.lib().fdl_sum_f32_static(x.data_ptr(), x.numel(), out.data_ptr(), out64.data_ptr(),
+                                                   side.cuda_stream), "captured")
+    cuda.cuda.current_stream().wait_stream(side)
+    for value in (0.25, 2.0, -1.0):
+        x.fill_(value)
+        out.zero_()
+        graph.replay()
+        cuda.cuda.synchronize()
+        assert out.item() == value * (1 << 22) and out64.item() == value * (1 << 22)
+    fdl.take_device_error()
+
+
 def test_the_maximum_size_itself_is_accepted(fdl, cuda):
     n = 1 << 30
     free, _ = cuda.cuda.mem_get_info()
