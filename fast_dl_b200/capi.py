@@ -42,6 +42,8 @@ PROTOTYPES = {
     "fdl_reduce_cols_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "fdl_sum_f32": (_int, [_vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     "fdl_sum_f32_static": (_int, [_vp, _i64, _vp, _vp, _vp]),
+    "fdl_debug_split_ticket": (_int, [_i64, _i64, _i64, C.c_uint, C.POINTER(C.c_int64), C.POINTER(C.c_int),
+                                      C.POINTER(C.c_int)]),
     "fdl_exchange_create": (_int, [_int, _int, C.POINTER(C.c_void_p)]),
     "fdl_exchange_local_handle": (_int, [_vp, C.c_char_p]),
     "fdl_exchange_connect": (_int, [_vp, C.c_char_p]),

@@ -1493,11 +1493,53 @@ rows_split_apply_kernel(const RowParams p, int phase, const float2* row_stats) {
 // k - lag; then the apply tasks of the last lag rows.  HINTS = false uses plain streaming loads
 // in both passes (tuning key rows_split_hints = 0, for comparison).
 struct SplitPlan {
+    int64_t rows;
     int nseg;
     int lag;
     unsigned int head;    // tickets before the first apply task: lag * nseg
     unsigned int middle;  // tickets of the rounds that hold both kinds: (rows - lag) * 2 * nseg
 };
+
+struct SplitTask {
+    int64_t row;
+    int seg;
+    bool apply;
+};
+
+// The plan of `rows` rows of `nseg` segments with the apply pass `lag` rows behind (1 <= lag <= rows).
+inline SplitPlan make_split_plan(int64_t rows, int64_t nseg, int64_t lag) {
+    SplitPlan plan;
+    plan.rows = rows;
+    plan.nseg = static_cast<int>(nseg);
+    plan.lag = static_cast<int>(lag);
+    plan.head = static_cast<unsigned int>(lag * nseg);
+    plan.middle = static_cast<unsigned int>((rows - lag) * 2 * nseg);
+    return plan;
+}
+
+// Ticket -> task; tickets run from 0 to 2 * rows * nseg - 1.  Host and device share this function
+// (fdl_debug_split_ticket lets a test on the host walk the whole enumeration).
+__host__ __device__ inline SplitTask split_decode(const SplitPlan& plan, unsigned int ticket) {
+    SplitTask task;
+    const unsigned int n = static_cast<unsigned int>(plan.nseg);
+    if (ticket < plan.head) {
+        task.row = ticket / n;
+        task.seg = static_cast<int>(ticket % n);
+        task.apply = false;
+    } else if (ticket < plan.head + plan.middle) {
+        const unsigned int u = ticket - plan.head;
+        const unsigned int k = u / (2u * n), j = u % (2u * n);
+        task.apply = j >= n;
+        task.row = task.apply ? k : static_cast<int64_t>(k) + plan.lag;
+        task.seg = static_cast<int>(task.apply ? j - n : j);
+    } else {
+        const unsigned int u = ticket - plan.head - plan.middle;
+        task.row = plan.rows - plan.lag + u / n;
+        task.seg = static_cast<int>(u % n);
+        task.apply = true;
+    }
+    return task;
+}
 
 template <class Op, bool MASKED, bool HINTS>
 __global__ void __launch_bounds__(kSplitThreads, (MASKED || !std::is_same<Op, SoftmaxOp>::value) ? 4 : 5)
@@ -1515,27 +1557,11 @@ rows_split_pipelined_kernel(const RowParams p, int phase, const SplitPlan plan, 
         if (ticket_shared == gridDim.x - 1) *queue = 0;
     }
     __syncthreads();
-    const unsigned int ticket = ticket_shared;
+    const SplitTask task = split_decode(plan, ticket_shared);
     const unsigned int n = static_cast<unsigned int>(plan.nseg);
-    int64_t row;
-    int seg;
-    bool apply;
-    if (ticket < plan.head) {
-        row = ticket / n;
-        seg = static_cast<int>(ticket % n);
-        apply = false;
-    } else if (ticket < plan.head + plan.middle) {
-        const unsigned int u = ticket - plan.head;
-        const unsigned int k = u / (2u * n), j = u % (2u * n);
-        apply = j >= n;
-        row = apply ? k : static_cast<int64_t>(k) + plan.lag;
-        seg = static_cast<int>(apply ? j - n : j);
-    } else {
-        const unsigned int u = ticket - plan.head - plan.middle;
-        row = p.rows - plan.lag + u / n;
-        seg = static_cast<int>(u % n);
-        apply = true;
-    }
+    const int64_t row = task.row;
+    const int seg = task.seg;
+    const bool apply = task.apply;
     const SplitSeg sg = split_segment<MASKED>(p, phase, row, seg);
     float4 v[kSplitNV];
     int okv[kSplitNV];
@@ -1578,11 +1604,7 @@ int launch_rows_split_pipelined(const RowParams& p, int phase, int64_t nseg, flo
     if (lag > p.rows) lag = p.rows;
     const int64_t tasks = 2 * p.rows * nseg;
     if (tasks > 2147483647 || p.rows >= kSplitMaxRows) return FDL_ERR_UNSUPPORTED;
-    SplitPlan plan;
-    plan.nseg = static_cast<int>(nseg);
-    plan.lag = static_cast<int>(lag);
-    plan.head = static_cast<unsigned int>(lag * nseg);
-    plan.middle = static_cast<unsigned int>((p.rows - lag) * 2 * nseg);
+    const SplitPlan plan = make_split_plan(p.rows, nseg, lag);
     const dim3 grid(static_cast<unsigned int>(tasks));
     if (tuning().rows_split_hints != 0)
         return launch_ex(rows_split_pipelined_kernel<Op, MASKED, true>, grid, dim3(kSplitThreads), 0, stream, dim3(1, 1, 1),
@@ -1860,6 +1882,19 @@ int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta
     p.cols = static_cast<int>(cols);
     p.eps = eps;
     return launch_rows_op<LayerNormOp>(p, as_stream(stream));
+}
+
+int fdl_debug_split_ticket(int64_t rows, int64_t segments, int64_t lag, unsigned int ticket, int64_t* row, int* segment,
+                           int* is_apply) {
+    if (rows < 1 || segments < 1 || lag < 1 || lag > rows || row == nullptr || segment == nullptr || is_apply == nullptr)
+        return FDL_ERR_INVALID_ARGUMENT;
+    if (2 * rows * segments > 2147483647 || rows >= kSplitMaxRows) return FDL_ERR_UNSUPPORTED;
+    if (ticket >= 2 * rows * segments) return FDL_ERR_INVALID_ARGUMENT;
+    const SplitTask task = split_decode(make_split_plan(rows, segments, lag), ticket);
+    *row = task.row;
+    *segment = task.seg;
+    *is_apply = task.apply ? 1 : 0;
+    return FDL_OK;
 }
 
 }  // extern "C"

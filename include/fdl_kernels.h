@@ -357,6 +357,16 @@ int fdl_layernorm_rows_f32(const float* x, const float* gamma, const float* beta
                            float* y, float* mean_out, float* rstd_out, int64_t rows,
                            int64_t cols, float eps, void* stream);
 
+/* Test aid, host only (no launch): the task that ticket `ticket` names in the one-launch form
+ * of softmax / layernorm on rows longer than a cluster holds -- `rows` rows of `segments` 32 KiB
+ * segments, the apply pass `lag` rows (1..rows) behind the statistics pass; tickets run from 0
+ * to 2 * rows * segments - 1.  The kernel decodes its tickets with the same function.  What the
+ * enumeration has to guarantee: every (row, segment, pass) exactly once, and every apply task
+ * of a row after all of that row's statistics tasks, so that a task only waits for tasks that
+ * CTAs which started earlier hold. */
+int fdl_debug_split_ticket(int64_t rows, int64_t segments, int64_t lag, unsigned int ticket, int64_t* row,
+                           int* segment, int* is_apply);
+
 /* ---- neighbours of the path (needed to stand in for the whole kernel library) ------------ */
 
 /* loss[0] = mean over rows of (log sum_c exp(logits[r,c]) - logits[r,label[r]]); rows whose
