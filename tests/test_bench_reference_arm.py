@@ -31,6 +31,23 @@ def test_reference_arm_prints_the_contract_line():
     assert e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
 
 
+def test_reference_arm_under_the_launcher_prints_one_line_from_rank_0():
+    """Launched like the GPU arm for N = 2: rank 0 measures and prints, the other rank leaves with 0."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29617", str(ROOT / "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [l for l in run.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1, run.stdout[-2000:]
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2
+    assert line["config"] == bench.workload_config(2, bench.ROWS)
+
+
 def test_algorithmic_bytes_of_the_step():
     sys.path.insert(0, str(ROOT))
     import bench
